@@ -1,7 +1,7 @@
 """The cache: a slot per sequence, keys and values per layer in pages, fixed-size
 state per sequence beside them.
 
-Layers with the same needs (kv heads, head size, window) form a *group* with
+Layers with the same needs (kv heads, head size, window, values of their own or not) form a *group* with
 pools and a page table of its own, so that, say, full-attention layers and
 sliding-window layers neither share pages nor waste them.  Pools are laid out
 [entries of the group, pages, kv_heads, page_size, head_dim] (one layer's slice
@@ -42,7 +42,8 @@ class _Group:
         self.pages = pages
         shape = (len(entries), num_pages, req.kv_heads, page_size, req.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        # values that are the keys (a cached latent): one pool, handed out as both
+        self.v = self.k if req.shared_kv else torch.zeros(shape, dtype=dtype, device=device)
         self.table_dev = torch.full((num_slots, max_pages_per_seq), -1, dtype=torch.int32, device=device)
 
     def upload(self) -> None:
@@ -73,7 +74,7 @@ class Cache:
         by_need: Dict[tuple, List[int]] = {}
         for i, r in enumerate(self.requests):
             if r is not None and r.kv_heads > 0:
-                by_need.setdefault((r.kv_heads, r.head_dim, r.window), []).append(i)
+                by_need.setdefault((r.kv_heads, r.head_dim, r.window, r.shared_kv), []).append(i)
         # the bookkeeping of slots, pages and lengths is one C++ object (csrc/host_cache.cpp)
         self.host = HostCache(num_slots, num_pages, self.max_pages_per_seq, page_size,
                               [need[2] for need in by_need])
@@ -138,7 +139,7 @@ class Cache:
 
     def bytes_per_token(self) -> int:
         es = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.entries) * g.req.kv_heads * g.req.head_dim * es for g in self.groups)
+        return sum((1 if g.req.shared_kv else 2) * len(g.entries) * g.req.kv_heads * g.req.head_dim * es for g in self.groups)
 
     def check(self) -> None:
         self.host.check()

@@ -7,7 +7,10 @@ in ``to_spec`` (a :class:`~.specs.ModelSpec`).  ``to_dict`` gives back the
 
 The architecture is chosen as thanhauco/rust-inference does it
 (src/models/config.rs:136-145): the first entry of ``architectures``, else
-``model_type``.
+``model_type``; a configuration that has neither may name it in ``architecture``.
+
+A configuration class may have ``with_checkpoint(model_dir)``: it returns the configuration with the
+sizes filled in that its config.json leaves to the shapes of the checkpoint's tensors.
 """
 from __future__ import annotations
 
@@ -43,9 +46,9 @@ def registered_architectures():
 
 def architecture_of(d: dict) -> str:
     archs = d.get("architectures") or []
-    name = archs[0] if archs else d.get("model_type")
-    if not name:
-        raise UnsupportedArchitecture("config.json names no architecture (architectures / model_type)")
+    name = archs[0] if archs else (d.get("model_type") or d.get("architecture"))
+    if not name or not isinstance(name, str):
+        raise UnsupportedArchitecture("config.json names no architecture (architectures / model_type / architecture)")
     return name
 
 

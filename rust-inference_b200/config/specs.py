@@ -26,6 +26,33 @@ class RMSNormSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """y = (x - mean) / sqrt(var + eps) * gain over ``size`` elements, var the mean squared deviation; no bias.
+
+    ``weight_name`` is the local name of the gain tensor; empty where the checkpoint names that tensor by the
+    norm's prefix alone."""
+    size: int
+    eps: float
+    weight_name: str = "weight"
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
+class RopePairsSpec:
+    """Rotary encoding of neighbouring pairs: elements 2i and 2i+1 of the first ``rotary_dim`` of a vector are turned
+    by position * f_i with f_i = theta^(-2i/rotary_dim).
+
+    ``yarn`` (None for none) holds (factor, original, fast, slow): with
+    d(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
+    hi = min(ceil(d(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is
+    f_i / factor * ramp_i + f_i * (1 - ramp_i), and cos and sin are both multiplied by 0.1 ln(factor) + 1."""
+    rotary_dim: int
+    theta: float
+    yarn: Optional[Tuple[float, float, float, float]] = None
+    kind: str = "rope_pairs"
+
+
+@dataclass(frozen=True)
 class RopeSpec:
     """Rotate-half rotary encoding of the first ``rotary_dim`` elements of a head.
 
@@ -69,6 +96,65 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are expanded from a cached latent.
+
+    Per head ``dim`` query/key elements without position and ``rot_dim`` with (``position`` turns them), values of
+    ``vdim``; the token's cache row is the RMS-normed latent (``kv_rank``, gain and ``eps``) and one rotated key part
+    that all heads share.  ``scale`` multiplies the whole score; ``window`` > 0 limits a query to the last
+    ``window`` keys; ``sink``: a learned term per head in the softmax's denominator; ``gate``: "head" (one sigmoid
+    gate per head), "element" (one per output element) or "" (none), from a projection of the mixer's input."""
+    hidden_size: int
+    num_heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    eps: float
+    position: object = NoPositionSpec()
+    window: int = 0
+    sink: bool = False
+    gate: str = ""
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class GLASpec:
+    """Gated linear attention: per head a state [dim, vdim] that each token decays per key channel
+    (sigmoid(low-rank projection + bias)^(1/tau)), feeds with k v^T and reads with q / sqrt(dim); the heads'
+    outputs are RMS-normed over ``vdim`` (one gain for all heads, ``eps``), gated with silu of a projection and
+    projected back.  ``decay_rank`` is the inner size of the decay's two projections."""
+    hidden_size: int
+    num_heads: int
+    dim: int
+    vdim: int
+    tau: float
+    decay_rank: int
+    eps: float
+    kind: str = "gla"
+
+
+@dataclass(frozen=True)
+class DenseFFSpec:
+    """down(act(up x)), no biases; ``activation``: "relu2" (the square of relu) or "gelu_tanh"."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "relu2"
+    kind: str = "dense"
+
+
+@dataclass(frozen=True)
+class HyperConnectionSpec:
+    """How a sublayer meets a residual kept as ``streams`` copies: it reads sum_s in[s] x_s, and its output y
+    turns the streams into x_t <- sum_s mix[s, t] x_s + out[t] y.  ``learned`` False: no tensors, in = out = [1]
+    and mix = [[1]] on one stream, which is the ordinary residual sum."""
+    streams: int
+    learned: bool = True
+    kind: str = "hyper"
+
+
+@dataclass(frozen=True)
 class SwiGLUSpec:
     """down(silu(gate x) * up x), no biases."""
     hidden_size: int
@@ -78,10 +164,13 @@ class SwiGLUSpec:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
-    """h[t] = table[ids[t]], no scaling."""
+    """h[t] = table[ids[t]] * scale; ``copies`` > 1: [tokens, copies, hidden] with every row that many times
+    (a residual kept as several streams starts with all of them equal)."""
     vocab_size: int
     hidden_size: int
     kind: str = "embedding"
+    scale: float = 1.0
+    copies: int = 1
 
 
 @dataclass(frozen=True)
@@ -110,6 +199,24 @@ class LayerSpec:
     ffn_norm: object
     names: Tuple[Tuple[str, str], ...] = ()
     arrangement: str = "prenorm"
+
+    def prefix(self, part: str) -> str:
+        return dict(self.names)[part]
+
+
+@dataclass(frozen=True)
+class StreamLayerSpec:
+    """One block over a residual of one or several streams (``arrangement`` "streams"): a norm and a mixer, then
+    (``ffn`` not None) a norm and a feed-forward, each met through its connection record (``mixer_link``,
+    ``ffn_link``: :class:`HyperConnectionSpec`).  ``names`` maps the parts to the prefixes of their tensors."""
+    mixer: object
+    mixer_norm: object
+    mixer_link: object
+    ffn: object = None
+    ffn_norm: object = None
+    ffn_link: object = None
+    names: Tuple[Tuple[str, str], ...] = ()
+    arrangement: str = "streams"
 
     def prefix(self, part: str) -> str:
         return dict(self.names)[part]

@@ -859,7 +859,7 @@ struct MergeCut {
 __global__ void __launch_bounds__(AD_MERGE_THREADS)
 attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                               bf16* __restrict__ out, const int* __restrict__ seq_len, int H, int max_chunks,
-                              int window, MergeCut cut, int* __restrict__ err) {
+                              int window, MergeCut cut, const float* __restrict__ sink, int* __restrict__ err) {
     constexpr int MW = AD_MERGE_THREADS / 32;            // warps
     constexpr int PER = (AD_DH + 127) / 128;             // float4 per lane
     const int h = blockIdx.x, b = blockIdx.y;
@@ -1001,6 +1001,8 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
     L = s_l[0];
 #pragma unroll
     for (int w = 1; w < MW; w++) L += s_l[w];
+    // a sink: one more term exp(sink[head]) in the denominator, with no key and no value (not scaled)
+    if (sink && L > 0.0f) L += exp2f(sink[h] * 1.4426950408889634f - M);
     for (int d = threadIdx.x; d < AD_DH; d += AD_MERGE_THREADS) {
         float a = s_acc[0][d];
 #pragma unroll
@@ -1066,10 +1068,12 @@ extern "C" int ri_attention_decode_parts(int max_chunks) {
 
 // q, out [seqs, H, Dh] bf16; o_part [seqs, H, parts, Dh] f32; ml_part [seqs, H, parts, 2] f32 with
 // parts = ri_attention_decode_parts(max_chunks).  max_chunks * 128 must cover the longest sequence of the step.
-extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* o_part,
-                                   float* ml_part, const int* page_table, const int* seq_slot, const int* seq_len,
-                                   int seqs, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
-                                   int max_chunks, float scale, int window, int* err_flag, cudaStream_t stream) {
+// sink [H] float32 or null: a learned term per head that joins the softmax's denominator only (the merge adds it).
+extern "C" int ri_attention_decode_sink(const void* q, const void* k_pool, const void* v_pool, void* out, float* o_part,
+                                        float* ml_part, const int* page_table, const int* seq_slot, const int* seq_len,
+                                        int seqs, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
+                                        int max_chunks, float scale, int window, const float* sink, int* err_flag,
+                                        cudaStream_t stream) {
     if (seqs == 0) return 0;
     RI_REQUIRE(Dh == AD_DH, "attention_decode: built for head_dim %d, called with %d", AD_DH, Dh);
     RI_REQUIRE(page_size == AD_PAGE, "attention_decode: pages of %d tokens, this kernel needs %d", page_size, AD_PAGE);
@@ -1126,7 +1130,7 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
         cut.KV = KV;
         cut.parts = a.parts;
         ri_launch_pdl(attention_decode_merge_kernel, dim3(H, seqs), dim3(AD_MERGE_THREADS), 0, stream,
-                      (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, cut, err_flag);
+                      (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, cut, sink, err_flag);
         RI_CHECK_LAUNCH("attention_decode_merge");
         return 0;
     }
@@ -1145,7 +1149,15 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
     chunks_of_128.KV = KV;
     chunks_of_128.parts = max_chunks;
     ri_launch_pdl(attention_decode_merge_kernel, dim3(H, seqs), dim3(AD_MERGE_THREADS), 0, stream,
-                  (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, chunks_of_128, err_flag);
+                  (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, chunks_of_128, sink, err_flag);
     RI_CHECK_LAUNCH("attention_decode_merge");
     return 0;
+}
+
+extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* o_part,
+                                   float* ml_part, const int* page_table, const int* seq_slot, const int* seq_len,
+                                   int seqs, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
+                                   int max_chunks, float scale, int window, int* err_flag, cudaStream_t stream) {
+    return ri_attention_decode_sink(q, k_pool, v_pool, out, o_part, ml_part, page_table, seq_slot, seq_len, seqs, H, KV, Dh,
+                                    mpps, page_size, num_pages, max_chunks, scale, window, nullptr, err_flag, stream);
 }

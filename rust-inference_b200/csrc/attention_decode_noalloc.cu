@@ -77,7 +77,7 @@ extern "C" int ri_attention_decode_noalloc(const void* q, const void* k_pool, co
     chunks_of_128.KV = KV;
     chunks_of_128.parts = max_chunks;
     attention_decode_merge_kernel<<<dim3(H, seqs), AD_MERGE_THREADS, 0, stream>>>(
-        o_part, ml_part, (bf16*)out, seq_len, H, max_chunks, window, chunks_of_128, err_flag);
+        o_part, ml_part, (bf16*)out, seq_len, H, max_chunks, window, chunks_of_128, nullptr, err_flag);
     RI_CHECK_LAUNCH("attention_decode_noalloc (merge)");
     return 0;
 }

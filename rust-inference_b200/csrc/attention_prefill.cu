@@ -66,7 +66,8 @@ __global__ void __launch_bounds__(32 * PF_WARPS)
 attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                          bf16* __restrict__ out, const int* __restrict__ page_table, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_len, int H, int KV, int mpps,
-                         int num_pages, float scale_log2, int window, int* __restrict__ err) {
+                         int num_pages, float scale_log2, int window, const float* __restrict__ sink,
+                         int* __restrict__ err) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PrefillSmem& sm = *reinterpret_cast<PrefillSmem*>(smem_raw);
     const int b = blockIdx.z, h = blockIdx.y;
@@ -191,6 +192,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     for (int r = 0; r < 2; r++) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        // a sink: one more term exp(sink[head]) in the denominator, with no key and no value (not scaled)
+        if (sink && m[r] != -FLT_MAX) l[r] += exp2f(sink[h] * 1.4426950408889634f - m[r]);
     }
 #pragma unroll
     for (int r = 0; r < 2; r++) {
@@ -208,12 +211,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 
 extern "C" int ri_attention_prefill_head_dim() { return PF_DH; }
 
-// q, out [tokens, H, Dh] bf16; max_new = the most tokens one sequence brings in this step
+// q, out [tokens, H, Dh] bf16; max_new = the most tokens one sequence brings in this step;
+// sink [H] float32 or null: a learned term per head that joins the softmax's denominator only
 extern "C" int ri_attention_prefill(const void* q, const void* k_pool, const void* v_pool, void* out,
                                     const int* page_table, const int* seq_slot, const int* seq_start,
                                     const int* seq_len, int seqs, int max_new, int H, int KV, int Dh, int mpps,
-                                    int page_size, int num_pages, float scale, int window, int* err_flag,
-                                    cudaStream_t stream) {
+                                    int page_size, int num_pages, float scale, int window, const float* sink,
+                                    int* err_flag, cudaStream_t stream) {
     if (seqs == 0 || max_new == 0) return 0;
     RI_REQUIRE(Dh == PF_DH, "attention_prefill: built for head_dim %d, called with %d", PF_DH, Dh);
     RI_REQUIRE(page_size == PF_PAGE, "attention_prefill: pages of %d tokens, this kernel needs %d", page_size, PF_PAGE);
@@ -230,7 +234,7 @@ extern "C" int ri_attention_prefill(const void* q, const void* k_pool, const voi
     dim3 grid((max_new + PF_BM - 1) / PF_BM, H, seqs);
     attention_prefill_kernel<<<grid, 32 * PF_WARPS, smem, stream>>>(
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, page_table, seq_slot, seq_start, seq_len,
-        H, KV, mpps, num_pages, scale * 1.4426950408889634f, window, err_flag);
+        H, KV, mpps, num_pages, scale * 1.4426950408889634f, window, sink, err_flag);
     RI_CHECK_LAUNCH("attention_prefill");
     return 0;
 }

@@ -146,7 +146,7 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, con
                       T* __restrict__ out, const int* __restrict__ page_table, const int* __restrict__ seq_slot,
                       const int* __restrict__ seq_start, const int* __restrict__ seq_len, int H, int KV, int Dh,
                       int mpps, int page_size, int num_pages, int tile_q, int group_chunk, float scale, int window,
-                      int* __restrict__ err) {
+                      const float* __restrict__ sink, int* __restrict__ err) {
     extern __shared__ __align__(16) float ar_smem[];
     const int b = blockIdx.z;
     const int t_begin = seq_start[b], n_new = seq_start[b + 1] - t_begin;
@@ -231,7 +231,9 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, con
     __syncthreads();
     for (int row = warp; row < rows; row += AR_WARPS) {
         const int i = row / ng, g = row - i * ng;
-        const float l = ls[row];
+        float l = ls[row];
+        // a sink: one more term exp(sink[head]) in the denominator, with no key and no value (not scaled)
+        if (sink && l > 0.0f) l += expf(sink[kvh * G + g0 + g] - ms[row]);
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;                 // no key at all: only after error 4
         T* dst = out + ((size_t)(t_begin + r_base + i) * H + kvh * G + g0 + g) * Dh;
         for (int d = lane; d < Dh; d += 32) st_f(dst + d, accs[(size_t)row * Dh + d] * inv);
@@ -256,8 +258,8 @@ static void ar_geometry(int G, int Dh, int max_new, bool vec4, int* tile_q, int*
 template <typename T, bool VEC4>
 static int ar_launch(const void* q, const void* k_pool, const void* v_pool, void* out, const int* page_table,
                      const int* seq_slot, const int* seq_start, const int* seq_len, int seqs, int max_new, int H, int KV,
-                     int Dh, int mpps, int page_size, int num_pages, float scale, int window, int* err_flag,
-                     cudaStream_t stream) {
+                     int Dh, int mpps, int page_size, int num_pages, float scale, int window, const float* sink,
+                     int* err_flag, cudaStream_t stream) {
     int tile_q, group_chunk;
     size_t smem;
     const int G = H / KV;
@@ -274,16 +276,17 @@ static int ar_launch(const void* q, const void* k_pool, const void* v_pool, void
     dim3 grid((max_new + tile_q - 1) / tile_q, (unsigned)gy, seqs);
     attention_rows_kernel<T, VEC4><<<grid, 32 * AR_WARPS, smem, stream>>>(
         (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, page_table, seq_slot, seq_start, seq_len, H, KV, Dh, mpps,
-        page_size, num_pages, tile_q, group_chunk, scale, window, err_flag);
+        page_size, num_pages, tile_q, group_chunk, scale, window, sink, err_flag);
     RI_CHECK_LAUNCH("attention_rows");
     return 0;
 }
 
 // q, out [tokens, H, Dh]; max_new = the most tokens one sequence brings in this step
+// sink [H] float32 or null: a learned term per head that joins the softmax's denominator only
 extern "C" int ri_attention_rows(const void* q, const void* k_pool, const void* v_pool, void* out, const int* page_table,
                                  const int* seq_slot, const int* seq_start, const int* seq_len, int seqs, int max_new,
                                  int H, int KV, int Dh, int mpps, int page_size, int num_pages, float scale, int window,
-                                 int dtype, int* err_flag, cudaStream_t stream) {
+                                 const float* sink, int dtype, int* err_flag, cudaStream_t stream) {
     if (seqs == 0 || max_new == 0) return 0;
     RI_REQUIRE(seqs > 0 && max_new > 0 && H > 0 && KV > 0 && Dh > 0 && page_size > 0 && mpps > 0, "attention_rows: bad sizes");
     RI_REQUIRE(H % KV == 0, "attention_rows: %d heads are not a multiple of %d kv heads", H, KV);
@@ -295,7 +298,7 @@ extern "C" int ri_attention_rows(const void* q, const void* k_pool, const void* 
     const uintptr_t align = f32 ? 15 : 7;
     const bool vec4 = Dh % 4 == 0 && (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & align) == 0;
 #define AR_GO(T, V) ar_launch<T, V>(q, k_pool, v_pool, out, page_table, seq_slot, seq_start, seq_len, seqs, max_new, H, KV, \
-                                    Dh, mpps, page_size, num_pages, scale, window, err_flag, stream)
+                                    Dh, mpps, page_size, num_pages, scale, window, sink, err_flag, stream)
     if (f32) return vec4 ? AR_GO(float, true) : AR_GO(float, false);
     return vec4 ? AR_GO(__nv_bfloat16, true) : AR_GO(__nv_bfloat16, false);
 #undef AR_GO

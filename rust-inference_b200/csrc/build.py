@@ -33,6 +33,9 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "rope_kv": ("rope_kv.cu", "common.cuh"),
     "attention_rows": ("attention_rows.cu", "common.cuh"),
     "linear_f32": ("linear_f32.cu", "common.cuh"),
+    "streams": ("streams.cu", "common.cuh"),
+    "latent_attention": ("latent_attention.cu", "common.cuh"),
+    "gla": ("gla.cu", "common.cuh"),
     "sampling": ("sampling.cu", "common.cuh"),
     "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh"),

@@ -10,7 +10,9 @@
 #include "linear_skinny_geometry.cuh"
 
 // ---------------------------------------------------------------------------
-// out[t, :] = float(table[ids[t], :])
+// out[t, c, :] = float(table[ids[t], :]) * scale for c = 0 .. copies-1
+// (one copy and scale 1: the plain gather; several copies start the residual streams of a
+// model with hyper-connections, which all begin as the embedding's output)
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void embed_load8(const float* p, float (&v)[8]) {
     const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
@@ -29,7 +31,7 @@ __device__ __forceinline__ void embed_load8(const __nv_bfloat16* p, float (&v)[8
 
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
-                                  int dim, int vocab, int* __restrict__ bad) {
+                                  int dim, int vocab, float scale, int copies, int* __restrict__ bad) {
     pdl_trigger();
     pdl_wait();
     int id = ids[blockIdx.x];
@@ -38,33 +40,46 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restri
         return;
     }
     const T* src = table + (size_t)id * dim;
-    float* dst = out + (size_t)blockIdx.x * dim;
+    float* dst = out + (size_t)blockIdx.x * copies * dim;
     if (dim % 8 == 0 && ((((uintptr_t)table | (uintptr_t)out)) & 15) == 0) {
         // 16 bytes per load: a row of 4,096 elements is one or two loads per thread instead of sixteen in a row
         for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
             float v[8];
             embed_load8(src + i, v);
-            *reinterpret_cast<float4*>(dst + i) = make_float4(v[0], v[1], v[2], v[3]);
-            *reinterpret_cast<float4*>(dst + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] *= scale;
+            for (int c = 0; c < copies; c++) {
+                *reinterpret_cast<float4*>(dst + (size_t)c * dim + i) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(dst + (size_t)c * dim + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
         }
         return;
     }
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ld_f(src + i);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = ld_f(src + i) * scale;
+        for (int c = 0; c < copies; c++) dst[(size_t)c * dim + i] = v;
+    }
 }
 
-extern "C" int ri_embed_rows(const int* ids, const void* table, float* out, int tokens, int dim, int vocab,
-                             int dtype, int* bad_flag, cudaStream_t stream) {
+extern "C" int ri_embed_rows_scaled(const int* ids, const void* table, float* out, int tokens, int dim, int vocab,
+                                    float scale, int copies, int dtype, int* bad_flag, cudaStream_t stream) {
     if (tokens == 0) return 0;
-    RI_REQUIRE(tokens > 0 && dim > 0 && vocab > 0, "embed_rows: bad sizes tokens=%d dim=%d vocab=%d", tokens, dim, vocab);
+    RI_REQUIRE(tokens > 0 && dim > 0 && vocab > 0 && copies > 0, "embed_rows: bad sizes tokens=%d dim=%d vocab=%d copies=%d",
+               tokens, dim, vocab, copies);
     int threads = dim >= 1024 ? 256 : 128;
     if (dtype == RI_DTYPE_F32)
-        ri_launch_pdl(embed_rows_kernel<float>, dim3(tokens), dim3(threads), 0, stream, ids, (const float*)table, out, dim, vocab, bad_flag);
+        ri_launch_pdl(embed_rows_kernel<float>, dim3(tokens), dim3(threads), 0, stream, ids, (const float*)table, out, dim, vocab, scale, copies, bad_flag);
     else if (dtype == RI_DTYPE_BF16)
-        ri_launch_pdl(embed_rows_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, dim, vocab, bad_flag);
+        ri_launch_pdl(embed_rows_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, dim, vocab, scale, copies, bad_flag);
     else
         RI_FAIL(-1, "embed_rows: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("embed_rows");
     return 0;
+}
+
+extern "C" int ri_embed_rows(const int* ids, const void* table, float* out, int tokens, int dim, int vocab,
+                             int dtype, int* bad_flag, cudaStream_t stream) {
+    return ri_embed_rows_scaled(ids, table, out, tokens, dim, vocab, 1.0f, 1, dtype, bad_flag, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -445,5 +460,91 @@ extern "C" int ri_silu_mul(const void* gu, void* out, int rows, int inter, int b
     else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, block, total);
     else RI_FAIL(-1, "silu_mul: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("silu_mul");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// out[i] = act(x[i]):  kind 0: relu(x)^2;  kind 1: gelu with the tanh form,
+// 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))).  float32 arithmetic, one rounding at the end.
+// ---------------------------------------------------------------------------
+#define RI_ACT_RELU2 0
+#define RI_ACT_GELU_TANH 1
+__device__ __forceinline__ float act_of(float x, int kind) {
+    if (kind == RI_ACT_RELU2) {
+        const float r = fmaxf(x, 0.0f);
+        return r * r;
+    }
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n, int kind) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        st_f(out + i, act_of(ld_f(x + i), kind));
+}
+
+template <typename T>
+__global__ void activation_vec8_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n8, int kind) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        Pack8<T> a, o;
+        a.load(x + 8 * i);
+#pragma unroll
+        for (int j = 0; j < 4; j++) o.set2(j, act_of(a.get(2 * j), kind), act_of(a.get(2 * j + 1), kind));
+        o.store(out + 8 * i);
+    }
+}
+
+extern "C" int ri_activation(const void* x, void* out, long long n, int kind, int dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    RI_REQUIRE(n > 0 && (kind == RI_ACT_RELU2 || kind == RI_ACT_GELU_TANH), "activation: bad arguments n=%lld kind=%d", n, kind);
+    RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "activation: unknown dtype %d", dtype);
+    if (n % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        const size_t n8 = (size_t)n / 8;
+        const unsigned blocks = (unsigned)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
+        if (dtype == RI_DTYPE_F32) ri_launch_pdl(activation_vec8_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)out, n8, kind);
+        else ri_launch_pdl(activation_vec8_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n8, kind);
+    } else {
+        const unsigned blocks = (unsigned)(((size_t)n + 255) / 256 < 148 * 16 ? ((size_t)n + 255) / 256 : 148 * 16);
+        if (dtype == RI_DTYPE_F32) ri_launch_pdl(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)out, (size_t)n, kind);
+        else ri_launch_pdl(activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, (size_t)n, kind);
+    }
+    RI_CHECK_LAUNCH("activation");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Gates on the heads of a mixer's output, in place:
+//   x[t, h, j] *= f(g[t, per_head ? h : h * width + j]),  f: 0 sigmoid, 1 silu
+// x [tokens, heads, width] is dense; g is a block of columns of a wider matrix (row pitch ldg).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void gate_heads_kernel(T* __restrict__ x, const T* __restrict__ g, long long ldg, int heads, int width,
+                                  int per_head, int fn, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t per_tok = (size_t)heads * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / per_tok;
+        const int c = (int)(i - t * per_tok);
+        const float z = ld_f(g + t * ldg + (per_head ? c / width : c));
+        const float s = 1.0f / (1.0f + expf(-z));
+        st_f(x + i, ld_f(x + i) * (fn == 1 ? z * s : s));
+    }
+}
+
+extern "C" int ri_gate_heads(void* x, const void* g, long long ldg, int tokens, int heads, int width, int per_head, int fn,
+                             int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    RI_REQUIRE(tokens > 0 && heads > 0 && width > 0 && (fn == 0 || fn == 1), "gate_heads: bad arguments");
+    const size_t total = (size_t)tokens * heads * width;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == RI_DTYPE_F32) ri_launch_pdl(gate_heads_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)g, ldg, heads, width, per_head, fn, total);
+    else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(gate_heads_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, (const __nv_bfloat16*)g, ldg, heads, width, per_head, fn, total);
+    else RI_FAIL(-1, "gate_heads: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("gate_heads");
     return 0;
 }

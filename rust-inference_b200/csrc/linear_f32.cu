@@ -12,7 +12,11 @@
 
 __global__ void __launch_bounds__(LF_THREADS)
 linear_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int M, int N, int K,
-                  int vec_ok) {
+                  int vec_ok, long long ldx, long long ldy, long long x_batch, long long w_batch, long long y_batch) {
+    // blockIdx.z: one product of a batch (a head); rows of x and y may lie ldx / ldy elements apart
+    x += (size_t)blockIdx.z * x_batch;
+    w += (size_t)blockIdx.z * w_batch;
+    y += (size_t)blockIdx.z * y_batch;
     __shared__ float xs[LF_BK][LF_BM + 4];
     __shared__ float ws[LF_BK][LF_BN + 4];
     int m0 = blockIdx.y * LF_BM, n0 = blockIdx.x * LF_BN;
@@ -29,14 +33,14 @@ linear_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
         float xv[4], wv[4];
         int gm = m0 + lrow, gn = n0 + lrow, gk = k0 + lk;
         if (vec_ok && gk + 3 < K) {
-            float4 a = gm < M ? *(const float4*)(x + (size_t)gm * K + gk) : make_float4(0, 0, 0, 0);
+            float4 a = gm < M ? *(const float4*)(x + (size_t)gm * ldx + gk) : make_float4(0, 0, 0, 0);
             float4 b = gn < N ? *(const float4*)(w + (size_t)gn * K + gk) : make_float4(0, 0, 0, 0);
             xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w;
             wv[0] = b.x; wv[1] = b.y; wv[2] = b.z; wv[3] = b.w;
         } else {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                xv[i] = (gm < M && gk + i < K) ? x[(size_t)gm * K + gk + i] : 0.0f;
+                xv[i] = (gm < M && gk + i < K) ? x[(size_t)gm * ldx + gk + i] : 0.0f;
                 wv[i] = (gn < N && gk + i < K) ? w[(size_t)gn * K + gk + i] : 0.0f;
             }
         }
@@ -65,7 +69,7 @@ linear_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             int gn = n0 + tx * 4 + j;
-            if (gn < N) y[(size_t)gm * N + gn] = acc[i][j];
+            if (gn < N) y[(size_t)gm * ldy + gn] = acc[i][j];
         }
     }
 }
@@ -76,7 +80,22 @@ extern "C" int ri_linear_f32(const float* x, const float* w, float* y, int M, in
     dim3 grid((N + LF_BN - 1) / LF_BN, (M + LF_BM - 1) / LF_BM);
     RI_REQUIRE(grid.y <= 65535, "linear_f32: too many rows (%d)", M);
     int vec_ok = (K % 4 == 0) && (((uintptr_t)x | (uintptr_t)w) % 16 == 0);
-    linear_f32_kernel<<<grid, LF_THREADS, 0, stream>>>(x, w, y, M, N, K, vec_ok);
+    linear_f32_kernel<<<grid, LF_THREADS, 0, stream>>>(x, w, y, M, N, K, vec_ok, K, N, 0, 0, 0);
     RI_CHECK_LAUNCH("linear_f32");
+    return 0;
+}
+
+// One product per head: y[m, h, :] = x[m, h, :] . W[h]^T with W [heads, N, K] dense, x rows of K elements that start
+// ldx apart per token and x_head apart per head, y likewise (ldy, y_head).  The arithmetic of an output element is
+// that of ri_linear_f32.
+extern "C" int ri_linear_heads_f32(const float* x, const float* w, float* y, int M, int heads, int N, int K, long long ldx,
+                                   long long x_head, long long ldy, long long y_head, cudaStream_t stream) {
+    if (M == 0 || N == 0 || heads == 0) return 0;
+    RI_REQUIRE(M > 0 && N > 0 && K > 0 && heads > 0, "linear_heads_f32: bad sizes M=%d heads=%d N=%d K=%d", M, heads, N, K);
+    dim3 grid((N + LF_BN - 1) / LF_BN, (M + LF_BM - 1) / LF_BM, heads);
+    RI_REQUIRE(grid.y <= 65535 && heads <= 65535, "linear_heads_f32: too many rows or heads (%d, %d)", M, heads);
+    int vec_ok = (K % 4 == 0) && (ldx % 4 == 0) && (x_head % 4 == 0) && (((uintptr_t)x | (uintptr_t)w) % 16 == 0);
+    linear_f32_kernel<<<grid, LF_THREADS, 0, stream>>>(x, w, y, M, N, K, vec_ok, ldx, ldy, x_head, (long long)N * K, y_head);
+    RI_CHECK_LAUNCH("linear_heads_f32");
     return 0;
 }

@@ -1,0 +1,113 @@
+// The norm in front of a sublayer for a model whose residual is kept as several streams
+// (hyper-connections), with everything around it in the same pass over the data.
+//
+// resid [n, S, dim] float32 holds S streams per token.  One block per output row does, element by element:
+//   1. the update that the sublayer before left pending (its output y [n, dim], not yet added):
+//          x'_t = sum over s of mix[s, t] x_s  +  outw[t] y        for every stream t, all from the old streams
+//      (written back to resid, unless only some rows are read: then nothing after this call reads resid);
+//   2. the sublayer's input  u = sum over t of read[t] x'_t        (read absent: the plain sum of the streams);
+//   3. the norm of the row u:  layer norm without bias  (u - mean) / sqrt(var + eps) * gain,  var = mean((u - mean)^2),
+//      or RMS norm  u / sqrt(mean(u^2) + eps) * gain.
+// With S = 1, mix = read = outw = [1] this is the ordinary pre-norm residual: x' = x + y, u = x'.
+// All of it is float32 whatever the compute type T of y and of the output; every sum has a fixed order
+// (streams ascending, then the block's tree over the row), so a row's result does not depend on the batch.
+#include "common.cuh"
+
+#define SN_MAX_STREAMS 16
+#define SN_KIND_LAYERNORM 0
+#define SN_KIND_RMSNORM 1
+
+template <typename T>
+__global__ void stream_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ mix,
+                                   const float* __restrict__ outw, const float* __restrict__ read,
+                                   const int* __restrict__ rows, const float* __restrict__ gain, T* __restrict__ out,
+                                   int S, int dim, float eps, int kind, int write_back) {
+    extern __shared__ float sn_row[];                 // [dim]
+    __shared__ float red[33];
+    __shared__ float s_mix[SN_MAX_STREAMS * SN_MAX_STREAMS], s_out[SN_MAX_STREAMS], s_read[SN_MAX_STREAMS];
+    pdl_trigger();
+    // the connection weights are parameters: read before the wait for the kernel in front
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[i] = mix ? mix[i] : (i / S == i % S ? 1.0f : 0.0f);
+    for (int i = threadIdx.x; i < S; i += blockDim.x) {
+        s_out[i] = outw ? outw[i] : 1.0f;
+        s_read[i] = read ? read[i] : 1.0f;
+    }
+    pdl_wait();
+    __syncthreads();
+    const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+    float* rp = resid + r * S * dim;
+    const T* dp = delta ? delta + r * dim : nullptr;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float x[SN_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < SN_MAX_STREAMS; s++)
+            if (s < S) x[s] = rp[(size_t)s * dim + i];
+        float u = 0.0f;
+        if (dp) {
+            const float y = ld_f(dp + i);
+#pragma unroll
+            for (int t = 0; t < SN_MAX_STREAMS; t++)
+                if (t < S) {
+                    float a = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < SN_MAX_STREAMS; s++)
+                        if (s < S) a = fmaf(s_mix[s * S + t], x[s], a);
+                    a = fmaf(s_out[t], y, a);
+                    if (write_back) rp[(size_t)t * dim + i] = a;
+                    u = fmaf(s_read[t], a, u);
+                }
+        } else {
+#pragma unroll
+            for (int t = 0; t < SN_MAX_STREAMS; t++)
+                if (t < S) u = fmaf(s_read[t], x[t], u);
+        }
+        sn_row[i] = u;
+        sum += kind == SN_KIND_LAYERNORM ? u : u * u;
+    }
+    float total = block_sum(sum, red);
+    float mean = 0.0f, inv;
+    if (kind == SN_KIND_LAYERNORM) {
+        mean = total / (float)dim;
+        float sq = 0.0f;
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+            const float d = sn_row[i] - mean;
+            sq += d * d;
+        }
+        inv = 1.0f / sqrtf(block_sum(sq, red) / (float)dim + eps);
+    } else {
+        inv = 1.0f / sqrtf(total / (float)dim + eps);
+    }
+    T* op = out + (size_t)blockIdx.x * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(op + i, (sn_row[i] - mean) * inv * gain[i]);
+}
+
+extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix, const float* outw, const float* read,
+                              const int* rows, const float* gain, void* out, int n_rows, int streams, int dim, float eps,
+                              int kind, int dtype, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    RI_REQUIRE(n_rows > 0 && dim > 0, "stream_norm: bad sizes rows=%d dim=%d", n_rows, dim);
+    RI_REQUIRE(streams >= 1 && streams <= SN_MAX_STREAMS, "stream_norm: %d streams (1 to %d are built)", streams, SN_MAX_STREAMS);
+    RI_REQUIRE(kind == SN_KIND_LAYERNORM || kind == SN_KIND_RMSNORM, "stream_norm: unknown norm %d", kind);
+    const size_t smem = (size_t)dim * sizeof(float);
+    RI_REQUIRE(smem <= 200 * 1024, "stream_norm: a row of %d elements does not fit in shared memory (limit 51200)", dim);
+    const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+    const int write_back = rows ? 0 : 1;
+    cudaError_t e = cudaSuccess;
+    if (dtype == RI_DTYPE_F32) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(stream_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RI_FAIL((int)e, "stream_norm: %s", cudaGetErrorString(e));
+        ri_launch_pdl(stream_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, resid, (const float*)delta, mix, outw,
+                      read, rows, gain, (float*)out, streams, dim, eps, kind, write_back);
+    } else if (dtype == RI_DTYPE_BF16) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(stream_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RI_FAIL((int)e, "stream_norm: %s", cudaGetErrorString(e));
+        ri_launch_pdl(stream_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, resid,
+                      (const __nv_bfloat16*)delta, mix, outw, read, rows, gain, (__nv_bfloat16*)out, streams, dim, eps, kind,
+                      write_back);
+    } else {
+        RI_FAIL(-1, "stream_norm: unknown dtype %d", dtype);
+    }
+    RI_CHECK_LAUNCH("stream_norm");
+    return 0;
+}

@@ -124,6 +124,8 @@ class Model:
     @classmethod
     def from_dir(cls, model_dir: str, dtype="bfloat16", device="cuda:0") -> "Model":
         cfg = load_config(model_dir)
+        if hasattr(cfg, "with_checkpoint"):
+            cfg = cfg.with_checkpoint(model_dir)         # sizes that only the tensors' shapes give
         spec = cfg.to_spec()
         model = cls(spec, dtype, device)
         model.config = cfg

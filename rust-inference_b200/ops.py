@@ -23,21 +23,29 @@ _F = ctypes.c_float
 
 _SIGNATURES = {
     ("elementwise", "ri_embed_rows"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    ("elementwise", "ri_embed_rows_scaled"): [_P, _P, _P, _I, _I, _I, _F, _I, _I, _P, _P],
+    ("elementwise", "ri_activation"): [_P, _P, _L, _I, _I, _P],
+    ("elementwise", "ri_gate_heads"): [_P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    ("streams", "ri_stream_norm"): [_P] * 8 + [_I, _I, _I, _F, _I, _I, _P],
+    ("latent_attention", "ri_latent_prep"): [_P, _L, _I, _I] + [_P] * 8 + [_F, _P] + [_I] * 11 + [_P, _P],
+    ("gla", "ri_gla_recurrent"): [_P, _L, _I, _I, _I, _P, _P, _F, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    ("gla", "ri_gla_head_norm_gate"): [_P, _P, _F, _P, _L, _P, _I, _I, _I, _I, _I, _P],
+    ("linear_f32", "ri_linear_heads_f32"): [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _P],
     ("elementwise", "ri_rmsnorm"): [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _P, _I, _I, _P],
     ("elementwise", "ri_add_rows"): [_P, _P, _L, _I, _P],
     ("elementwise", "ri_silu_mul"): [_P, _P, _I, _I, _I, _I, _P],
     ("rope_kv", "ri_qk_norm_rope_append"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 9 + [_P, _P],
-    ("attention_rows", "ri_attention_rows"): [_P] * 8 + [_I] * 8 + [_F, _I, _I, _P, _P],
+    ("attention_rows", "ri_attention_rows"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _I, _P, _P],
     ("linear_f32", "ri_linear_f32"): [_P, _P, _P, _I, _I, _I, _P],
     ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _P, _I, _P],
     ("sampling", "ri_sample_work_bytes"): [_I, _I],
     ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P, _P, _P],
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
-    ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
+    ("attention_decode", "ri_attention_decode_sink"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P, _P],
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _P],
-    ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
+    ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P, _P],
 }
 DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
 MAX_FAST_HEAD_DIM = 256
@@ -181,15 +189,199 @@ ERROR_TEXT = {1: "token id outside the vocabulary", 2: "cache write to an unmapp
 
 
 # ---------------------------------------------------------------------------------------
-def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
-    """float32 rows ``table[ids]``: [tokens, dim]."""
+def embed(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0, copies: int = 1) -> torch.Tensor:
+    """float32 rows ``table[ids] * scale``: [tokens, dim], or [tokens, copies, dim] with every row ``copies`` times
+    (the streams of a residual that is kept several times over all start as the embedding)."""
     _need(ids, "ids", torch.int32)
     _need(table, "table")
     tokens, (vocab, dim) = ids.numel(), table.shape
-    out = torch.empty((tokens, dim), dtype=torch.float32, device=table.device)
-    _call("elementwise", "ri_embed_rows", ids.data_ptr(), table.data_ptr(), out.data_ptr(), tokens, dim, vocab,
-          _code(table.dtype), error_flag(table.device).data_ptr(), _stream())
+    shape = (tokens, dim) if copies == 1 else (tokens, copies, dim)
+    out = torch.empty(shape, dtype=torch.float32, device=table.device)
+    _call("elementwise", "ri_embed_rows_scaled", ids.data_ptr(), table.data_ptr(), out.data_ptr(), tokens, dim, vocab,
+          float(scale), int(copies), _code(table.dtype), error_flag(table.device).data_ptr(), _stream())
     return out
+
+
+NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
+
+
+def stream_norm(resid: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype, kind: str = "layernorm",
+                delta: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                out_w: Optional[torch.Tensor] = None, read: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The norm in front of a sublayer over a residual of S streams ``resid`` [n, S, dim] (float32).
+
+    First the pending update: with ``delta`` [n, dim] (the output of the sublayer before, compute dtype) every
+    stream t becomes sum_s mix[s, t] x_s + out_w[t] delta (``mix`` absent: the identity; ``out_w`` absent: ones),
+    written back into ``resid`` unless ``rows`` is given.  Then the input u = sum_t read[t] x_t (``read`` absent:
+    the plain sum) is normed with ``gain`` (``kind``: "layernorm" without bias, or "rmsnorm").  With ``rows``
+    (int32 indices) only those rows are read, in that order.  Returns [n or len(rows), dim] in ``out_dtype``."""
+    _need(resid, "resid", torch.float32)
+    if resid.dim() != 3:
+        raise KernelError(f"stream_norm: resid must be [tokens, streams, dim], got {tuple(resid.shape)}")
+    n, S, dim = resid.shape
+    _need(gain, "gain", torch.float32, (dim,))
+    if delta is not None:
+        _need(delta, "delta", out_dtype, (n, dim))
+    for t, name, shape in ((mix, "mix", (S, S)), (out_w, "out_w", (S,)), (read, "read", (S,))):
+        if t is not None:
+            _need(t, name, torch.float32, shape)
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    n_out = n if rows is None else rows.numel()
+    out = torch.empty((n_out, dim), dtype=out_dtype, device=resid.device)
+    _call("streams", "ri_stream_norm", resid.data_ptr(), _ptr(delta), _ptr(mix), _ptr(out_w), _ptr(read), _ptr(rows),
+          gain.data_ptr(), out.data_ptr(), n_out, S, dim, float(eps), NORM_KINDS[kind], _code(out_dtype), _stream())
+    return out
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1}
+
+
+def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """Element by element: "relu2" relu(x)^2, "gelu_tanh" 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))."""
+    _need(x, "x")
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation {kind!r} is not built (known: {', '.join(sorted(ACTIVATIONS))})")
+    out = torch.empty_like(x)
+    _call("elementwise", "ri_activation", x.data_ptr(), out.data_ptr(), x.numel(), ACTIVATIONS[kind], _code(x.dtype), _stream())
+    return out
+
+
+def _columns(t: torch.Tensor, name: str, dtype) -> int:
+    """``t`` is a block of columns of a dense matrix (a slice ``m[:, a:b]``): returns its row pitch in elements."""
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype or t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be columns of a {dtype} matrix, got {t.dtype} with strides {t.stride()}")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def gate_heads(x: torch.Tensor, g: torch.Tensor, fn: str = "sigmoid") -> torch.Tensor:
+    """In place: x[t, h, j] *= f(g[t, h]) when ``g`` has one column per head, or f(g[t, h * width + j]) when it has
+    one per element; f "sigmoid" or "silu".  ``g`` may be a block of columns of a wider matrix."""
+    _need(x, "x")
+    tokens, heads, width = x.shape
+    ldg = _columns(g, "g", x.dtype)
+    if g.shape[0] != tokens or g.shape[1] not in (heads, heads * width):
+        raise KernelError(f"gate_heads: gates {tuple(g.shape)} do not fit {tuple(x.shape)}")
+    per_head = 1 if g.shape[1] == heads else 0
+    _call("elementwise", "ri_gate_heads", x.data_ptr(), g.data_ptr(), ldg, tokens, heads, width, per_head,
+          {"sigmoid": 0, "silu": 1}[fn], _code(x.dtype), _stream())
+    return x
+
+
+def linear_heads(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """One product per head: y[t, h, :] = w[h] x[t, h, :] for x [tokens, H, K] (any strides with dense last
+    dimension, e.g. a slice of a projection), w [H, N, K] dense; y [tokens, H, N] dense.
+    float32: this package's FMA kernel (the arithmetic of ``linear``); bfloat16: the library's batched product."""
+    if x.dim() != 3 or w.dim() != 3 or x.shape[1] != w.shape[0] or x.shape[2] != w.shape[2]:
+        raise KernelError(f"linear_heads: x {tuple(x.shape)} and w {tuple(w.shape)} do not fit")
+    _need(w, "w", x.dtype)
+    M, H, K = x.shape
+    N = w.shape[1]
+    if not x.is_cuda or (K > 1 and x.stride(2) != 1):
+        raise KernelError("linear_heads: x must be a CUDA tensor whose last dimension is dense")
+    y = torch.empty((M, H, N), dtype=x.dtype, device=x.device)
+    if M == 0:
+        return y
+    if x.dtype == torch.float32:
+        _call("linear_f32", "ri_linear_heads_f32", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, H, N, K,
+              x.stride(0), x.stride(1), H * N, N, _stream())
+        return y
+    if x.dtype != torch.bfloat16:
+        raise KernelError(f"linear_heads: dtype {x.dtype}")
+    torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=y.transpose(0, 1))
+    return y
+
+
+def latent_prep(proj: torch.Tensor, q_col: int, dkv_col: int, qa: torch.Tensor, heads: int, dim: int, rot: int, rank: int,
+                gain: torch.Tensor, eps: float, rope_table: Optional[torch.Tensor], pool: Optional[torch.Tensor],
+                page_table: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor, seq_slot: torch.Tensor,
+                write: bool = True) -> torch.Tensor:
+    """Latent attention between its projections and the attention over the cache.  ``proj`` [tokens, N] holds the
+    heads' queries ([dim plain, rot to rotate] each) from column ``q_col`` and the down projection (rank + rot) from
+    ``dkv_col``; ``qa`` [tokens, H, rank] the plain query parts already multiplied by the key up-projection.  Appends
+    [RMS-normed latent, rotated shared key part] to ``pool`` [pages, 1, page_size, rank + rot] and returns the
+    query rows [tokens, H, rank + rot].  Rotation turns neighbouring pairs by ``rope_table`` [positions, rot/2, 2]."""
+    _need(proj, "proj")
+    tokens, ld = proj.shape
+    _need(qa, "qa", proj.dtype, (tokens, heads, rank))
+    _need(gain, "gain", torch.float32, (rank,))
+    Dk = rank + rot
+    if q_col + heads * (dim + rot) > ld or dkv_col + Dk > ld:
+        raise KernelError("latent_prep: the projection is narrower than its columns")
+    rows = 0
+    if rot:
+        if rope_table is None:
+            raise KernelError("latent_prep: a rotated part needs the table of angles")
+        _need(rope_table, "rope_table", torch.float32)
+        if rope_table.dim() != 3 or rope_table.shape[1] != rot // 2 or rope_table.shape[2] != 2:
+            raise KernelError(f"rope table must be [positions, {rot // 2}, 2], got {tuple(rope_table.shape)}")
+        rows = rope_table.shape[0]
+    else:
+        rows = 1 << 30
+    if write:
+        if pool is None:
+            raise KernelError("latent_prep: appending needs the cache pool")
+        _need(pool, "pool", proj.dtype)
+        pages, kvh, page_size, dk = pool.shape
+        if kvh != 1 or dk != Dk:
+            raise KernelError(f"latent_prep: pool {tuple(pool.shape)} does not fit one row of {Dk} per token")
+    else:
+        pages, page_size = 1, 1
+    _need(page_table, "page_table", torch.int32)
+    for t, n in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (seq_slot, "seq_slot")):
+        _need(t, n, torch.int32)
+    qf = torch.empty((tokens, heads, Dk), dtype=proj.dtype, device=proj.device)
+    _call("latent_attention", "ri_latent_prep", proj.data_ptr(), ld, int(q_col), int(dkv_col), qa.data_ptr(), qf.data_ptr(),
+          _ptr(pool) if write else None, page_table.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_slot.data_ptr(),
+          gain.data_ptr(), float(eps), _ptr(rope_table), rows, tokens, heads, dim, rot, rank, page_table.shape[1], page_size,
+          pages, 1 if write else 0, _code(proj.dtype), error_flag(proj.device).data_ptr(), _stream())
+    return qf
+
+
+def gla_recurrent(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, bias: torch.Tensor, tau: float,
+                  qscale: float, state: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, heads: int, dim: int,
+                  vdim: int) -> torch.Tensor:
+    """Gated linear attention over the step's new tokens.  Per (sequence, head) the state S [dim, vdim] (float32, in
+    ``state`` [slots, H, dim, vdim], updated in place) goes S <- diag(a_t) S + k_t v_t^T with the decay
+    a_t = sigmoid(z_t + bias)^(1/tau) per key channel, and o_t = S^T (q_t qscale).  q, k, v are columns of ``proj``
+    [tokens, N] from ``q_col``, ``k_col``, ``v_col`` (head after head); ``z`` [tokens, H*dim].  Returns o [tokens, H, vdim]
+    in float32."""
+    _need(proj, "proj")
+    tokens, ld = proj.shape
+    _need(z, "z", proj.dtype, (tokens, heads * dim))
+    _need(bias, "bias", torch.float32, (heads * dim,))
+    _need(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError(f"gla_recurrent: state {tuple(state.shape)} does not fit {heads} heads of {dim} x {vdim}")
+    seqs = seq_slot.numel()
+    _need(seq_slot, "seq_slot", torch.int32, (seqs,))
+    _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
+    if max(q_col, k_col) + heads * dim > ld or v_col + heads * vdim > ld:
+        raise KernelError("gla_recurrent: the projection is narrower than its columns")
+    o = torch.empty((tokens, heads, vdim), dtype=torch.float32, device=proj.device)
+    _call("gla", "ri_gla_recurrent", proj.data_ptr(), ld, int(q_col), int(k_col), int(v_col), z.data_ptr(), bias.data_ptr(),
+          float(tau), float(qscale), state.data_ptr(), o.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seqs, heads,
+          dim, vdim, _code(proj.dtype), _stream())
+    return o
+
+
+def head_norm_gate(o: torch.Tensor, gain: torch.Tensor, eps: float, g: torch.Tensor, out_dtype: torch.dtype,
+                   fn: str = "silu") -> torch.Tensor:
+    """y[t, h, :] = rmsnorm(o[t, h, :]) * gain * f(g[t, h*width ..]) for float32 o [tokens, H, width]; ``g`` [tokens,
+    H*width] may be a block of columns of a wider matrix of the compute dtype.  Returns [tokens, H*width]."""
+    _need(o, "o", torch.float32)
+    tokens, H, width = o.shape
+    _need(gain, "gain", torch.float32, (width,))
+    ldg = _columns(g, "g", out_dtype)
+    if tuple(g.shape) != (tokens, H * width):
+        raise KernelError(f"head_norm_gate: gates {tuple(g.shape)} do not fit {tuple(o.shape)}")
+    y = torch.empty((tokens, H * width), dtype=out_dtype, device=o.device)
+    _call("gla", "ri_gla_head_norm_gate", o.data_ptr(), gain.data_ptr(), float(eps), g.data_ptr(), ldg, y.data_ptr(), tokens,
+          H, width, {"sigmoid": 0, "silu": 1}[fn], _code(out_dtype), _stream())
+    return y
 
 
 def _weight_hint(then: Optional[torch.Tensor], tokens: int) -> Optional[torch.Tensor]:
@@ -404,13 +596,22 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
     return q
 
 
+def _sink(sink: Optional[torch.Tensor], heads: int) -> Optional[int]:
+    if sink is None:
+        return None
+    _need(sink, "sink", torch.float32, (heads,))
+    return sink.data_ptr()
+
+
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               seq_slot: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_new: int, scale: float,
-              window: int = 0) -> torch.Tensor:
+              window: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of the step's new tokens (q [tokens, H, Dh], sequences back to back as
     ``seq_start`` says) over the paged cache, which already holds their keys and values: float32 or
     bfloat16, any head size up to 512, any page size.  Every (token, head) is computed in one fixed
-    order that depends on its own position only, so the result does not depend on the step's cutting."""
+    order that depends on its own position only, so the result does not depend on the step's cutting.
+    ``sink`` [H] (float32): exp(sink[h]) joins head h's softmax denominator, with no key and no value.
+    ``v_pool`` may be ``k_pool`` itself (values that are the keys: latent attention)."""
     _need(q, "q")
     tokens, H, Dh = q.shape
     pages, KV, page_size, dh = k_pool.shape
@@ -426,7 +627,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     out = torch.empty_like(q)
     _call("attention_rows", "ri_attention_rows", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
           page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(), seqs, int(max_new),
-          H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window), _code(q.dtype),
+          H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window), _sink(sink, H), _code(q.dtype),
           error_flag(q.device).data_ptr(), _stream())
     return out
 
@@ -438,13 +639,13 @@ def fast_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int) 
 
 def _decode_parts(head_dim: int, chunks: int) -> int:
     """Partial results per (sequence, head) that the decode attention's scratch memory must have room for."""
-    _, lib = _fn("attention_decode", "ri_attention_decode", {"RI_HEAD_DIM": head_dim})
+    _, lib = _fn("attention_decode", "ri_attention_decode_sink", {"RI_HEAD_DIM": head_dim})
     return int(lib.ri_attention_decode_parts(int(chunks)))
 
 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                      seq_slot: torch.Tensor, seq_len: torch.Tensor, scale: float, window: int,
-                     max_len: int) -> torch.Tensor:
+                     max_len: int, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of one new token per sequence (q [seqs, H, Dh], bfloat16) over the
     paged cache, keys split into chunks of ``DECODE_CHUNK``; ``max_len`` bounds the
     sequences' lengths after this step and sizes the scratch memory."""
@@ -465,16 +666,16 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     o_part = torch.empty((seqs, H, parts, Dh), dtype=torch.float32, device=q.device)
     ml_part = torch.empty((seqs, H, parts, 2), dtype=torch.float32, device=q.device)
     out = torch.empty_like(q)
-    _call("attention_decode", "ri_attention_decode", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+    _call("attention_decode", "ri_attention_decode_sink", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), o_part.data_ptr(), ml_part.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(),
           seq_len.data_ptr(), seqs, H, KV, Dh, page_table.shape[1], page_size, pages, chunks, float(scale),
-          int(window), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+          int(window), _sink(sink, H), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
     return out
 
 
 def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                       seq_slot: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_new: int,
-                      scale: float, window: int) -> torch.Tensor:
+                      scale: float, window: int, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of the step's new tokens (q [tokens, H, Dh], bfloat16, sequences back
     to back as ``seq_start`` says) over the paged cache, which already holds their keys
     and values; ``max_new`` is the most tokens one sequence brings."""
@@ -493,8 +694,8 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
     _need(seq_len, "seq_len", torch.int32, (seqs,))
     out = torch.empty_like(q)
-    if Dh in TCGEN05_HEAD_DIMS and not _NO_TCGEN05:
-        # head sizes of 64 and 128: the tcgen05 / tensor-memory kernel
+    if Dh in TCGEN05_HEAD_DIMS and not _NO_TCGEN05 and sink is None:
+        # head sizes of 64 and 128: the tcgen05 / tensor-memory kernel (it has no sink term: those go below)
         _call("attention_prefill_tc", "ri_attention_prefill_tc", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
               out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
               q.shape[0], seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
@@ -503,7 +704,7 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     _call("attention_prefill", "ri_attention_prefill", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
           seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
-          error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+          _sink(sink, H), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
     return out
 
 

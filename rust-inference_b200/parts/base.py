@@ -78,14 +78,26 @@ class CacheRequest:
     """What a mixer needs stored per sequence.
 
     Keys and values: ``kv_heads`` x ``head_dim`` per token (0 for none), all of
-    them (``window`` 0) or the last ``window``.  Fixed-size state:
-    ``state_shape`` per sequence (empty for none), zeroed when a slot is given
-    out."""
+    them (``window`` 0) or the last ``window``.  ``shared_kv``: the values are the
+    keys (a latent that serves as both), so one pool is kept and handed out as both.
+    Fixed-size state: ``state_shape`` per sequence (empty for none), zeroed when a
+    slot is given out."""
     kv_heads: int = 0
     head_dim: int = 0
     window: int = 0
     state_shape: tuple = ()
     state_dtype: torch.dtype = torch.float32
+    shared_kv: bool = False
+
+
+@dataclass
+class Pending:
+    """A sublayer's output that has not joined the residual yet, for a residual kept as several streams: the norm in
+    front of the next sublayer applies x_t <- sum_s mix[s, t] x_s + out[t] y while it reads the streams
+    (``mix`` None: the identity; ``out`` None: ones)."""
+    y: torch.Tensor
+    mix: Optional[torch.Tensor] = None
+    out: Optional[torch.Tensor] = None
 
 
 class Part:

@@ -55,6 +55,29 @@ class PreNormBlock(BlockBase):
         return resid, self.ffn(x, ctx)
 
 
+@register_block("streams")
+class StreamBlock(BlockBase):
+    """A pre-norm layer over a residual of one or several streams [tokens, streams, width]: each sublayer reads the
+    norm of the streams' weighted sum and its output joins the streams by its connection's weights (``parts/link.py``).
+    The feed-forward half is optional.  The update is left pending, as in "prenorm": the next norm does it."""
+
+    @classmethod
+    def slots(cls, spec):
+        out = [("mixer_norm", "norm", spec.mixer_norm), ("mixer_link", "link", spec.mixer_link),
+               ("mixer", "mixer", spec.mixer)]
+        if spec.ffn is not None:
+            out += [("ffn_norm", "norm", spec.ffn_norm), ("ffn_link", "link", spec.ffn_link), ("ffn", "ffn", spec.ffn)]
+        return tuple(out)
+
+    def __call__(self, resid, delta, ctx, cache):
+        x = self.mixer_norm(resid, delta, read=self.mixer_link.read)
+        delta = self.mixer_link.pending(self.mixer(x, ctx, cache))
+        if self.spec.ffn is None:
+            return resid, delta
+        x = self.ffn_norm(resid, delta, read=self.ffn_link.read)
+        return resid, self.ffn_link.pending(self.ffn(x, ctx))
+
+
 def norm_before(norm, resid, delta, reader):
     """``norm(resid + delta)`` for the part ``reader``; a norm that takes hints is told which matrix is read next."""
     if norm.takes_hint:

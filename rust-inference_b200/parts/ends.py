@@ -1,6 +1,7 @@
 """The two ends of the model: token ids in, logits out.
 
-``embedding``: h[t] = table[ids[t]] as float32 rows of the residual stream, no scaling; an id
+``embedding``: h[t] = table[ids[t]] as float32 rows of the residual stream (times the record's
+``scale``, 1 by default, and repeated ``copies`` times for a residual kept as several streams); an id
 outside the table is reported through the error word (thanhauco/rust-inference
 src/ops/embedding.rs:10-42).
 
@@ -40,7 +41,7 @@ class TokenEmbedding(Part):
         return self.table.numel() * self.table.element_size()
 
     def __call__(self, ids, ctx=None):
-        return ops.embed(ids, self.table)
+        return ops.embed(ids, self.table, getattr(self.spec, "scale", 1.0), getattr(self.spec, "copies", 1))
 
 
 @register_head("linear")

@@ -1,0 +1,45 @@
+"""How a sublayer meets the residual.
+
+``hyper``: hyper-connections.  The residual is kept as S streams x_1 .. x_S (all equal to the embedding's output at
+the start; the model's final norm reads their sum).  A sublayer reads u = sum_s in[s] x_s, and its output y turns
+the streams, all at once from the old ones, into x_t <- sum_s mix[s, t] x_s + out[t] y (``mix`` is indexed
+[from, to]).  The three tensors ``in`` [S], ``out`` [S] and ``mix`` [S, S] stay float32.  A record with
+``learned`` False has no tensors and one stream: u = x and x <- x + y, the ordinary residual sum.
+
+The part computes nothing itself: the norm in front of the next sublayer does the update while it reads the streams
+(``ops.stream_norm``); this part holds the weights and wraps an output as :class:`~.base.Pending`.
+"""
+from __future__ import annotations
+
+from .base import Part, Pending
+from .registry import ParamInfo, register_link
+
+
+@register_link("hyper")
+class HyperConnection(Part):
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.streams < 1:
+            raise ValueError(f"a residual needs at least one stream, got {spec.streams}")
+        if not spec.learned and spec.streams != 1:
+            raise ValueError("a connection without weights is the plain residual sum and has one stream")
+        self.read = self.mix = self.out = None
+
+    @classmethod
+    def param_infos(cls, spec):
+        if not spec.learned:
+            return {}
+        S = spec.streams
+        return {"in": ParamInfo((S,), "gain"), "out": ParamInfo((S,), "gain"), "mix": ParamInfo((S, S), "gain")}
+
+    def load(self, tensors):
+        if self.spec.learned:
+            self.read, self.out, self.mix = tensors["in"], tensors["out"], tensors["mix"].contiguous()
+
+    def weight_bytes(self):
+        return 0 if self.read is None else 4 * (self.read.numel() + self.out.numel() + self.mix.numel())
+
+    def pending(self, y) -> Pending:
+        return Pending(y, self.mix, self.out)

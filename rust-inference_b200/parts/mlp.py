@@ -43,3 +43,36 @@ class SwiGLU(FeedForward):
             z = ops.linear_swiglu(x, self.gate_up, self.block)
         with section("mlp down"):
             return ops.linear(z, self.down)
+
+
+@register_ffn("dense")
+class DenseFF(FeedForward):
+    """down(act(up x)), no biases; the activation ("relu2": the square of relu, or "gelu_tanh") is a record field."""
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r} is not built (known: {', '.join(sorted(ops.ACTIVATIONS))})")
+
+    @classmethod
+    def param_infos(cls, spec):
+        D, I = spec.hidden_size, spec.intermediate_size
+        return {"up": ParamInfo((I, D)), "down": ParamInfo((D, I))}
+
+    def load(self, tensors):
+        self.up, self.down = tensors["up"].contiguous(), tensors["down"].contiguous()
+
+    def weight_bytes(self):
+        return (self.up.numel() + self.down.numel()) * self.up.element_size()
+
+    def reads_first(self):
+        return self.up
+
+    def __call__(self, x, ctx):
+        with section("mlp up"):
+            z = ops.linear(x, self.up)
+        with section("mlp act"):
+            z = ops.activation(z, self.spec.activation)
+        with section("mlp down"):
+            return ops.linear(z, self.down)

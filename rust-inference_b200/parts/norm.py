@@ -1,12 +1,18 @@
 """RMSNorm: y = x * (1 / sqrt(mean(x^2) + eps)) * gain, all in float32
 (thanhauco/rust-inference src/ops/norm.rs:7-62).  Reads the float32 residual
 stream, adds the pending output of the previous part on the way if there is
-one, and writes the normed rows in the compute dtype."""
+one, and writes the normed rows in the compute dtype.
+
+LayerNorm (no bias): y = (x - mean) / sqrt(var + eps) * gain with var the mean squared
+deviation, float32.  It reads a residual of one or several streams ([tokens, dim] or
+[tokens, streams, dim]): the pending output joins the streams by its connection's weights
+(:class:`~.base.Pending`) and the row that is normed is the streams' weighted sum (``read``;
+absent: their plain sum), all in the same kernel."""
 from __future__ import annotations
 
 from .. import ops
 from ..profiler import section
-from .base import Norm
+from .base import Norm, Pending
 from .registry import ParamInfo, register_norm
 
 
@@ -28,3 +34,30 @@ class RMSNorm(Norm):
     def __call__(self, resid, delta=None, rows=None, then=None):
         with section("rmsnorm"):
             return ops.rmsnorm(resid, self.gain, self.spec.eps, self.env.dtype, delta=delta, rows=rows, then=then)
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    graph_safe = True
+    takes_hint = True
+
+    @classmethod
+    def param_infos(cls, spec):
+        return {spec.weight_name: ParamInfo((spec.size,), "gain")}
+
+    def load(self, tensors):
+        self.gain = tensors[self.spec.weight_name]
+
+    def weight_bytes(self):
+        return self.gain.numel() * 4
+
+    def __call__(self, resid, delta=None, rows=None, then=None, read=None):
+        streams = resid if resid.dim() == 3 else resid.view(resid.shape[0], 1, resid.shape[1])
+        y = mix = out = None
+        if isinstance(delta, Pending):
+            y, mix, out = delta.y, delta.mix, delta.out
+        elif delta is not None:
+            y = delta
+        with section("layernorm"):
+            return ops.stream_norm(streams, self.gain, self.spec.eps, self.env.dtype, "layernorm", delta=y, mix=mix,
+                                   out_w=out, read=read, rows=rows)

@@ -9,9 +9,17 @@ The attention kernel applies the table itself (``fused_table``).  Parts with
 the same rotary size, base, scaling and device share one table (a model's layers
 usually do), so it is held once, not once per layer.
 
+``rope_pairs``: neighbouring elements (2i, 2i+1) are turned, not the two halves, optionally with YaRN's
+blended frequencies and its factor on cos and sin (:class:`~..config.specs.RopePairsSpec` has the rule).  The
+frequencies are evaluated in float64 and rounded to float32, the angle is the float32 product with the float32
+position, cos and sin of it are evaluated in float64 and rounded once.  The table has the same layout
+[positions, rot/2, 2]; the kernels of the mixers that name this kind pair the elements accordingly.
+
 ``none``: nothing.
 """
 from __future__ import annotations
+
+import math
 
 import numpy as np
 import torch
@@ -50,6 +58,54 @@ class Rope(PositionEncoding):
         ang = (pos[:, None] * self.inv_freq()[None, :]).astype(np.float32).astype(np.float64)
         scale = float(self.spec.scaling)
         table = np.stack([np.cos(ang) * scale, np.sin(ang) * scale], axis=-1).astype(np.float32)
+        self._table = _shared_tables[key] = torch.from_numpy(table).to(self.env.device).contiguous()
+
+    def fused_table(self):
+        return self._table
+
+
+@register_position("rope_pairs")
+class RopePairs(PositionEncoding):
+    graph_safe = True
+    pairs = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
+            raise ValueError(f"rotary_dim {spec.rotary_dim} must be positive and even")
+        self._table = None
+
+    def frequencies(self):
+        """(float32 frequencies [rot/2], factor on cos and sin)."""
+        rot, theta = self.spec.rotary_dim, float(self.spec.theta)
+        i = np.arange(rot // 2, dtype=np.float64)
+        f = theta ** (-2.0 * i / rot)
+        mult = 1.0
+        if self.spec.yarn is not None:
+            factor, original, fast, slow = (float(v) for v in self.spec.yarn)
+
+            def where(turns):
+                return rot * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+            lo = max(math.floor(where(fast)), 0)
+            hi = min(math.ceil(where(slow)), rot - 1)
+            ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+            mult = 0.1 * math.log(factor) + 1.0
+        return f.astype(np.float32), mult
+
+    def prepare(self, max_positions: int) -> None:
+        if self._table is not None and self._table.shape[0] >= max_positions:
+            return
+        key = (str(self.env.device), "pairs", int(self.spec.rotary_dim), float(self.spec.theta), self.spec.yarn)
+        shared = _shared_tables.get(key)
+        if shared is not None and shared.shape[0] >= max_positions:
+            self._table = shared
+            return
+        f, mult = self.frequencies()
+        pos = np.arange(max_positions, dtype=np.float32)
+        ang = (pos[:, None] * f[None, :]).astype(np.float32).astype(np.float64)
+        table = np.stack([np.cos(ang) * mult, np.sin(ang) * mult], axis=-1).astype(np.float32)
         self._table = _shared_tables[key] = torch.from_numpy(table).to(self.env.device).contiguous()
 
     def fused_table(self):

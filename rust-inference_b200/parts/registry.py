@@ -16,7 +16,7 @@ from dataclasses import dataclass
 from typing import Callable, Dict, Tuple
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {},
-                                           "embedding": {}, "head": {}}
+                                           "embedding": {}, "head": {}, "link": {}}
 
 
 @dataclass(frozen=True)
@@ -53,6 +53,11 @@ def register_norm(kind: str):
 
 def register_position(kind: str):
     return _register("position", kind)
+
+
+def register_link(kind: str):
+    """How a sublayer reads from and writes to the residual (the weights of a hyper-connection)."""
+    return _register("link", kind)
 
 
 def register_block(kind: str):

@@ -36,9 +36,11 @@ def run(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None, o
     os.makedirs(out_dir, exist_ok=True)
     if model is None:
         model = Model.from_dir(model_dir, dtype=dtype, device=device)
-    # every live request holds at least 64 tokens of the budget, so this many can be live at once
-    max_seqs = max(1, min(max_tokens // 64, 4096))
-    engine = Engine(model, max_tokens=max(max_tokens, PAGE_SIZE), max_seqs=max_seqs)
+    # ``max_tokens`` counts the tokens that live requests hold, not the pages: a request of a few tokens still takes
+    # a slot and a page per cache group, so there are slots for requests of 8 tokens and a spare page for each
+    max_seqs = max(8, min(max_tokens // 8, 1024))
+    engine = Engine(model, max_tokens=max(max_tokens, PAGE_SIZE) + max_seqs * PAGE_SIZE, max_seqs=max_seqs,
+                    max_seq_len=max(max_tokens, PAGE_SIZE))
     slots = {}
     for line in lines:
         line = line.strip()
@@ -75,7 +77,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+                    help="most tokens live requests hold at any time")
     a = ap.parse_args(argv)
     return run(a.model, a.dtype, a.out, a.max_tokens)
 

@@ -13,11 +13,106 @@ import numpy as np
 import torch
 
 __all__ = ["embed", "rmsnorm", "add_rows", "silu_mul", "linear_swiglu", "linear", "qk_norm_rope_append", "attention", "argmax",
-           "sample", "mark_seen"]
+           "sample", "mark_seen", "stream_norm", "activation", "gate_heads", "linear_heads", "latent_prep", "gla_recurrent",
+           "head_norm_gate"]
 
 
-def embed(ids, table):
-    return table[ids.long()].float()
+def embed(ids, table, scale=1.0, copies=1):
+    x = table[ids.long()].float() * scale
+    return x if copies == 1 else x[:, None, :].repeat(1, copies, 1)
+
+
+def stream_norm(resid, gain, eps, out_dtype, kind="layernorm", delta=None, mix=None, out_w=None, read=None, rows=None):
+    n, S, dim = resid.shape
+    x = resid if rows is None else resid[rows.long()]
+    if delta is not None:
+        y = (delta if rows is None else delta[rows.long()]).float()
+        m = torch.eye(S) if mix is None else mix
+        o = torch.ones(S) if out_w is None else out_w
+        x = torch.einsum("st,nsd->ntd", m, x) + o[None, :, None] * y[:, None, :]
+        if rows is None:
+            resid.copy_(x)
+    r = torch.ones(S) if read is None else read
+    u = torch.einsum("s,nsd->nd", r, x)
+    if kind == "layernorm":
+        mu = u.mean(-1, keepdim=True)
+        var = ((u - mu) ** 2).mean(-1, keepdim=True)
+        return ((u - mu) / torch.sqrt(var + eps) * gain).to(out_dtype)
+    return (u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * gain).to(out_dtype)
+
+
+def activation(x, kind):
+    f = x.float()
+    if kind == "relu2":
+        return (torch.clamp(f, min=0.0) ** 2).to(x.dtype)
+    return (0.5 * f * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (f + 0.044715 * f ** 3)))).to(x.dtype)
+
+
+def _gate(z, fn):
+    s = 1.0 / (1.0 + torch.exp(-z))
+    return z * s if fn == "silu" else s
+
+
+def gate_heads(x, g, fn="sigmoid"):
+    tokens, heads, width = x.shape
+    gz = _gate(g.float(), fn)
+    gz = gz[:, :, None] if g.shape[1] == heads else gz.view(tokens, heads, width)
+    x.copy_((x.float() * gz).to(x.dtype))
+    return x
+
+
+def linear_heads(x, w):
+    return torch.einsum("thk,hnk->thn", x.double(), w.double()).to(x.dtype).contiguous()
+
+
+def latent_prep(proj, q_col, dkv_col, qa, heads, dim, rot, rank, gain, eps, rope_table, pool, page_table, tok_seq, tok_pos,
+                seq_slot, write=True):
+    T = proj.shape[0]
+    p = proj.float()
+
+    def turn(v):                                   # [T, ..., rot]
+        cs = rope_table[tok_pos.long()]
+        shape = (T,) + (1,) * (v.dim() - 2) + (rot // 2,)
+        c, s = cs[..., 0].view(shape), cs[..., 1].view(shape)
+        a, b = v[..., 0::2], v[..., 1::2]
+        return torch.stack([a * c - b * s, b * c + a * s], dim=-1).flatten(-2)
+
+    down = p[:, dkv_col:dkv_col + rank + rot]
+    c = down[:, :rank]
+    c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * gain
+    row = torch.cat([c, turn(down[:, rank:]) if rot else down[:, rank:]], dim=-1)
+    if write:
+        P = pool.shape[2]
+        for t in range(T):
+            pos = int(tok_pos[t])
+            page = int(page_table[int(seq_slot[int(tok_seq[t])]), pos // P])
+            assert page >= 0, "write to an unmapped page"
+            pool[page, 0, pos % P, :] = row[t].to(pool.dtype)
+    q = p[:, q_col:q_col + heads * (dim + rot)].view(T, heads, dim + rot)
+    qr = turn(q[..., dim:]) if rot else q[..., dim:]
+    return torch.cat([qa.float(), qr], dim=-1).to(proj.dtype).contiguous()
+
+
+def gla_recurrent(proj, q_col, k_col, v_col, z, bias, tau, qscale, state, seq_slot, seq_start, heads, dim, vdim):
+    T = proj.shape[0]
+    p = proj.float()
+    q = p[:, q_col:q_col + heads * dim].view(T, heads, dim) * qscale
+    k = p[:, k_col:k_col + heads * dim].view(T, heads, dim)
+    v = p[:, v_col:v_col + heads * vdim].view(T, heads, vdim)
+    a = torch.exp(torch.nn.functional.logsigmoid(z.float() + bias) / tau).view(T, heads, dim)
+    o = torch.zeros(T, heads, vdim)
+    for b in range(seq_slot.numel()):
+        S = state[int(seq_slot[b])]
+        for t in range(int(seq_start[b]), int(seq_start[b + 1])):
+            S.copy_(a[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :])
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    return o
+
+
+def head_norm_gate(o, gain, eps, g, out_dtype, fn="silu"):
+    tokens, H, width = o.shape
+    y = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * gain
+    return (y * _gate(g.float(), fn).view(tokens, H, width)).view(tokens, H * width).to(out_dtype)
 
 
 def rmsnorm(resid, gain, eps, out_dtype, delta=None, rows=None, then=None):
@@ -88,7 +183,7 @@ def qk_norm_rope_append(qkv, num_heads, num_kv_heads, head_dim, q_gain, k_gain, 
     return q.to(qkv.dtype).contiguous()
 
 
-def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_new, scale, window=0):
+def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_new, scale, window=0, sink=None):
     T, H, Dh = q.shape
     KV, P = k_pool.shape[1], k_pool.shape[2]
     G = H // KV
@@ -106,7 +201,10 @@ def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_n
             vv = v_pool[pages, :, (idx % P).long(), :].float()
             for h in range(H):
                 s = (kk[:, h // G, :] @ q[t, h].float()) * scale
-                p = torch.softmax(s, dim=0)
+                if sink is None:
+                    p = torch.softmax(s, dim=0)
+                else:
+                    p = torch.softmax(torch.cat([s, sink[h].view(1)]), dim=0)[:-1]
                 out[t, h] = p @ vv[:, h // G, :]
     return out.to(q.dtype)
 
