@@ -17,11 +17,16 @@
 #define SN_KIND_LAYERNORM 0
 #define SN_KIND_RMSNORM 1
 
-template <typename T>
-__global__ void stream_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ mix,
-                                   const float* __restrict__ outw, const float* __restrict__ read,
-                                   const int* __restrict__ rows, const float* __restrict__ gain, T* __restrict__ out,
-                                   int S, int dim, float eps, int kind, int write_back) {
+// NS: the number of streams when it is 1 to 8 (the loops over streams are then unrolled over registers), 0: any
+// number up to SN_MAX_STREAMS, read at run time.
+template <typename T, int NS>
+__global__ void __launch_bounds__(512)
+stream_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ mix,
+                   const float* __restrict__ outw, const float* __restrict__ read, const int* __restrict__ rows,
+                   const float* __restrict__ gain, T* __restrict__ out, int streams, int dim, float eps, int kind,
+                   int write_back) {
+    constexpr int SN_CAP = NS ? NS : SN_MAX_STREAMS;
+    const int S = NS ? NS : streams;
     extern __shared__ float sn_row[];                 // [dim]
     __shared__ float red[33];
     __shared__ float s_mix[SN_MAX_STREAMS * SN_MAX_STREAMS], s_out[SN_MAX_STREAMS], s_read[SN_MAX_STREAMS];
@@ -39,19 +44,19 @@ __global__ void stream_norm_kernel(float* __restrict__ resid, const T* __restric
     const T* dp = delta ? delta + r * dim : nullptr;
     float sum = 0.0f;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        float x[SN_MAX_STREAMS];
+        float x[SN_CAP];
 #pragma unroll
-        for (int s = 0; s < SN_MAX_STREAMS; s++)
+        for (int s = 0; s < SN_CAP; s++)
             if (s < S) x[s] = rp[(size_t)s * dim + i];
         float u = 0.0f;
         if (dp) {
             const float y = ld_f(dp + i);
 #pragma unroll
-            for (int t = 0; t < SN_MAX_STREAMS; t++)
+            for (int t = 0; t < SN_CAP; t++)
                 if (t < S) {
                     float a = 0.0f;
 #pragma unroll
-                    for (int s = 0; s < SN_MAX_STREAMS; s++)
+                    for (int s = 0; s < SN_CAP; s++)
                         if (s < S) a = fmaf(s_mix[s * S + t], x[s], a);
                     a = fmaf(s_out[t], y, a);
                     if (write_back) rp[(size_t)t * dim + i] = a;
@@ -59,7 +64,7 @@ __global__ void stream_norm_kernel(float* __restrict__ resid, const T* __restric
                 }
         } else {
 #pragma unroll
-            for (int t = 0; t < SN_MAX_STREAMS; t++)
+            for (int t = 0; t < SN_CAP; t++)
                 if (t < S) u = fmaf(s_read[t], x[t], u);
         }
         sn_row[i] = u;
@@ -93,21 +98,32 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
     RI_REQUIRE(smem <= 200 * 1024, "stream_norm: a row of %d elements does not fit in shared memory (limit 51200)", dim);
     const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
     const int write_back = rows ? 0 : 1;
+    RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "stream_norm: unknown dtype %d", dtype);
     cudaError_t e = cudaSuccess;
-    if (dtype == RI_DTYPE_F32) {
-        if (smem > 48 * 1024) e = cudaFuncSetAttribute(stream_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) RI_FAIL((int)e, "stream_norm: %s", cudaGetErrorString(e));
-        ri_launch_pdl(stream_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, resid, (const float*)delta, mix, outw,
-                      read, rows, gain, (float*)out, streams, dim, eps, kind, write_back);
-    } else if (dtype == RI_DTYPE_BF16) {
-        if (smem > 48 * 1024) e = cudaFuncSetAttribute(stream_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) RI_FAIL((int)e, "stream_norm: %s", cudaGetErrorString(e));
-        ri_launch_pdl(stream_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, resid,
-                      (const __nv_bfloat16*)delta, mix, outw, read, rows, gain, (__nv_bfloat16*)out, streams, dim, eps, kind,
-                      write_back);
-    } else {
-        RI_FAIL(-1, "stream_norm: unknown dtype %d", dtype);
+#define SN_GO(T, NS)                                                                                                     \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024)                                                                                            \
+            e = cudaFuncSetAttribute(stream_norm_kernel<T, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        if (e != cudaSuccess) RI_FAIL((int)e, "stream_norm: %s", cudaGetErrorString(e));                                 \
+        ri_launch_pdl(stream_norm_kernel<T, NS>, dim3(n_rows), dim3(threads), smem, stream, resid, (const T*)delta, mix,  \
+                      outw, read, rows, gain, (T*)out, streams, dim, eps, kind, write_back);                             \
+    } while (0)
+#define SN_BY_STREAMS(T)                                                                                                 \
+    switch (streams) {                                                                                                   \
+        case 1: SN_GO(T, 1); break;                                                                                      \
+        case 2: SN_GO(T, 2); break;                                                                                      \
+        case 3: SN_GO(T, 3); break;                                                                                      \
+        case 4: SN_GO(T, 4); break;                                                                                      \
+        case 5: SN_GO(T, 5); break;                                                                                      \
+        case 6: SN_GO(T, 6); break;                                                                                      \
+        case 7: SN_GO(T, 7); break;                                                                                      \
+        case 8: SN_GO(T, 8); break;                                                                                      \
+        default: SN_GO(T, 0); break;                                                                                     \
     }
+    if (dtype == RI_DTYPE_F32) SN_BY_STREAMS(float)
+    else SN_BY_STREAMS(__nv_bfloat16)
+#undef SN_BY_STREAMS
+#undef SN_GO
     RI_CHECK_LAUNCH("stream_norm");
     return 0;
 }

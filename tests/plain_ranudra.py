@@ -75,7 +75,10 @@ def latent_attention(h, w, m, eps, sink=False, gate="head"):
     H, dim, rot, vdim, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     pos = np.arange(n)
     rcfg = m.get("rot") or {}
-    freqs, mult = rotary_frequencies(rot, float(rcfg["base"]), rcfg.get("scaling"))
+    if rot:
+        freqs, mult = rotary_frequencies(rot, float(rcfg["base"]), rcfg.get("scaling"))
+    else:
+        freqs, mult = np.zeros(0, dtype=F64), 1.0             # no rotated part at all
     q = (h @ w["q"].T).reshape(n, H, dim + rot)
     q_plain, q_turn = q[..., :dim], rotate_pairs(q[..., dim:], pos, freqs, mult)
     down = h @ w["dkv"].T
