@@ -18,6 +18,13 @@ steps end at exactly 4,096 tokens.  One JSON line is printed:
   points     decode tokens a second at batch 1 and 64 (device-timed), and the same through
              the Python entry point (e2e_b1, e2e_b64)
 
+    python bench.py --design ranudra [--size small|large]
+
+measures the Ranudra design (latent attention, gated linear attention, hyper-connections) at layer sizes that
+resemble a real model's, beside a Qwen3 model of the same width, depth and parameter count: decode at batch 8 and a
+prompt step of 2,048 tokens, device-timed, and the device time of every section of both steps from eager runs with
+the section timers on, with the bytes or flops of the sections that have a roofline.  One JSON line.
+
     python bench.py --workload 14b | 32b
 
 runs the workloads that the reference's figures are quoted on for the larger sizes, whole
@@ -244,6 +251,150 @@ def run_workload(a) -> int:
     return 0
 
 
+# ---- the Ranudra design beside a Qwen3 model of equal size ---------------------------------------------------------
+DESIGN_SIZES = {
+    # width, feed-forward width, heads, layers (a third each of gla, latent attention with YaRN, latent attention with a sink)
+    "small": dict(width=2048, ff=8192, heads=16, layers=6, vocab=32768),
+    "large": dict(width=4096, ff=16384, heads=32, layers=6, vocab=32768),
+}
+
+
+def ranudra_config(z) -> dict:
+    D, H = z["width"], z["heads"]
+    vd = D // H
+    gla = {"type": "gla", "mixer": {"heads": H, "dim": 64, "vdim": vd, "tau": 16.0, "decay_rank": 16},
+           "mlp": {"kind": "dense", "ff": z["ff"]}}
+    rot = {"base": 500000.0, "dims": 64}
+    la = {"type": "latent_attention",
+          "mixer": {"heads": H, "dim": 128, "rot_dim": 64, "vdim": vd, "kv_rank": 192, "scale": 192 ** -0.5,
+                    "mask": {"size": 4096},
+                    "rot": dict(rot, scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})},
+          "mlp": {"kind": "dense", "ff": z["ff"]}}
+    la2 = {"type": "latent_attention_2",
+           "mixer": {"heads": H, "dim": 128, "rot_dim": 64, "vdim": vd, "kv_rank": 192, "scale": 192 ** -0.5,
+                     "mask": {"size": 1024}, "rot": rot},
+           "mlp": {"kind": "dense", "ff": z["ff"]}}
+    return {"architecture": "Ranudra", "vocab": z["vocab"], "width": D, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "streams": 4, "layers": [gla, la, la2] * (z["layers"] // 3)}
+
+
+def qwen3_like(z) -> dict:
+    inter = -(-(2 * z["ff"] // 3) // 256) * 256          # three matrices of SwiGLU against two: the same parameters
+    return dict(QWEN3_8B, num_hidden_layers=z["layers"], hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=max(1, z["heads"] // 4), head_dim=z["width"] // z["heads"], intermediate_size=inter,
+                vocab_size=z["vocab"], tie_word_embeddings=True)
+
+
+def run_design(a) -> int:
+    import torch
+
+    from rust_inference_b200 import ops, profiler
+    from rust_inference_b200.engine import Engine, Entry, Model
+
+    z = DESIGN_SIZES[a.size]
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    B, ctx, T = a.batch, a.context, a.prefill_tokens
+    K, Wm = a.steps, max(3, min(a.warmup, 16))
+    gen = torch.Generator().manual_seed(0)
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+    out = {}
+    for label, cfg in (("ranudra", ranudra_config(z)), ("qwen3", qwen3_like(z))):
+        model = Model.from_random(cfg, seed=1, dtype="bfloat16", device=dev)
+        V = model.spec.vocab_size
+        engine = Engine(model, max_tokens=B * ctx + T + 64, max_seqs=B + 1, max_seq_len=max(ctx, T))
+        for g in engine.cache.groups:
+            g.k.normal_(0.0, 0.5)
+            if g.v is not g.k:
+                g.v.normal_(0.0, 0.5)
+
+        def decode(steps, warm, timed_sections=False):
+            slots = [engine.new_sequence() for _ in range(B)]
+            engine.cache.extend([(s, ctx - (steps + warm)) for s in slots])
+            engine.cache.upload()
+            toks = torch.randint(0, V, (steps + warm, B), generator=gen).tolist()
+            for i in range(warm):
+                ops.argmax(engine.step([Entry(s, [t]) for s, t in zip(slots, toks[i])]))
+            torch.cuda.synchronize()
+            n0 = ops.launch_count()
+            if timed_sections:
+                profiler.reset()
+                profiler.enable(True)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t_a = time.time()
+            e0.record()
+            for i in range(warm, warm + steps):
+                ops.argmax(engine.step([Entry(s, [t]) for s, t in zip(slots, toks[i])]))
+            e1.record()
+            torch.cuda.synchronize()
+            windows.append((t_a, time.time()))
+            sections = None
+            if timed_sections:
+                sections = {n: round(sec / steps * 1e6, 2) for n, sec, _ in profiler.snapshot()}
+                profiler.enable(False)
+            for s in slots:
+                engine.release(s)
+            engine.check_device_errors()
+            return e0.elapsed_time(e1) / steps, ops.launch_count() - n0, sections
+
+        def prefill(timed_sections=False):
+            prompt = torch.randint(0, V, (T,), generator=gen).tolist()
+            times, sections = [], None
+            for i in range(3 + 3):
+                s = engine.new_sequence()
+                if timed_sections and i == 5:
+                    profiler.reset()
+                    profiler.enable(True)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t_a = time.time()
+                e0.record()
+                engine.step([Entry(s, prompt)])
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    times.append(e0.elapsed_time(e1))
+                    windows.append((t_a, time.time()))
+                if timed_sections and i == 5:
+                    sections = {n: round(sec * 1e6, 1) for n, sec, _ in profiler.snapshot()}
+                    profiler.enable(False)
+                engine.release(s)
+            return statistics.median(times[:2] if timed_sections else times), sections
+
+        ms_step, launches, _ = decode(K, Wm)
+        pre_ms, _ = prefill()
+        # where the time goes: the same steps run eagerly with a pair of events around every section
+        engine.use_graphs = False
+        _, _, dec_sections = decode(8, 3, timed_sections=True)
+        _, pre_sections = prefill(timed_sections=True)
+        out[label] = {
+            "decode_tok_s": round(B * 1e3 / ms_step, 1), "decode_ms_per_step": round(ms_step, 4),
+            "prefill_tok_s": round(T * 1e3 / pre_ms, 1), "prefill_ms": round(pre_ms, 3),
+            "weight_bytes": model.weight_bytes(), "cache_bytes_per_token": engine.cache.bytes_per_token(),
+            "decode_launches": launches // K, "graph_replays": engine.graph_replays,
+            "decode_sections_us": dec_sections, "prefill_sections_us": pre_sections,
+        }
+        del engine, model
+        torch.cuda.empty_cache()
+    clocks.stop()
+    r = out["ranudra"]
+    line = {
+        "metric": f"decode tok/s at batch {B}, context {ctx} (Ranudra, {a.size} layer shapes, bf16)",
+        "value": r["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm,
+        "ms_per_step": r["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random-init weights, uniform random token ids", "design": "ranudra",
+        "config": dict(z, size=a.size, global_batch=B, seq_len=ctx, prefill_tokens=T, parallelism="1 GPU", peaks=peak_src,
+                       beside="a Qwen3 model of the same width, depth and parameter count"),
+        "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops},
+        "ranudra": r, "qwen3": out["qwen3"], "clocks": clocks.summary(windows), "gpu_launches": r["decode_launches"] * K,
+        "impl": "ours",
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     global CONTEXT, PREFILL_TOKENS, METRIC
     ap = argparse.ArgumentParser()
@@ -263,6 +414,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS),
                     help="run a whole workload of the larger sizes through LLM.generate instead of the default line")
+    ap.add_argument("--design", choices=["ranudra"],
+                    help="measure another design beside a Qwen3 model of equal size instead of the default line")
+    ap.add_argument("--size", default="small", choices=sorted(DESIGN_SIZES), help="layer sizes of --design")
     a = ap.parse_args()
     a.steps_given = a.steps is not None
     if a.steps is None:
@@ -278,6 +432,8 @@ def main() -> int:
     CONTEXT, PREFILL_TOKENS = a.context, a.prefill_tokens
     if a.workload:
         return run_workload(a)
+    if a.design:
+        return run_design(a)
     if a.warmup < 3:
         a.warmup = 3
 

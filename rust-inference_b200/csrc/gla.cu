@@ -6,8 +6,8 @@
 // then per head  y_t = o_t / sqrt(mean_j(o_t[j]^2) + eps) * gain * silu(g_t)   (`gla_head_norm_gate`).
 //
 // `gla_recurrent`: a block owns one (sequence, head, tile of value columns j) and walks the sequence's new
-// tokens in order; a thread owns one column of the state, which lives in shared memory ([dim][tile]), and is
-// loaded from / stored to the sequence's slot of the state tensor at the ends.  The decay is computed as
+// tokens in order; a thread owns one column of the state (in registers for heads of up to 128 key channels, else in
+// shared memory), loaded from / stored to the sequence's slot of the state tensor at the ends.  The decay is computed as
 // exp(log_sigmoid(z) / tau) with float32 functions; q, k, v and z come from bfloat16 or float32 projections and
 // are widened once.  A token's result depends on the tokens before it only through the state, so prompts,
 // pieces of prompts and single tokens give the same bits.
@@ -18,6 +18,7 @@
 #include "common.cuh"
 
 #define GLA_TILE 64
+#define GLA_COLS 128            // threads per block of the register kernel
 
 __device__ __forceinline__ float gla_decay(float z, float inv_tau) {
     // log(sigmoid(z)) = min(z, 0) - log1p(exp(-|z|))
@@ -25,6 +26,151 @@ __device__ __forceinline__ float gla_decay(float z, float inv_tau) {
     return expf(ls * inv_tau);
 }
 
+// The kernel for heads of up to 128 key channels.  Four neighbouring lanes share one value column of the state: each
+// keeps a quarter of the column's key channels in registers (DIMC / 4 of them, DIMC the head's key channels rounded
+// up to 32, 64 or 128; lane p of the four has channels 16 c + 4 p .. + 3 for c = 0, 1, ..; channels past `dim` hold
+// zeros and stay zero), so a block of 128 threads owns 32 columns.  The block stages the decay, key and scaled query
+// of GROUP tokens in shared memory (two buffers): the loads of the next group are on their way while the current
+// group is computed, and the decay's exponentials are taken when a group is stored.  A group that the sequence does
+// not fill is padded with tokens of decay 1 and key 0, which leave the state as it is, bit for bit.  A lane walks
+// its channels in the outer loop and the group's tokens in the inner one,
+//     S[d] = a_g[d] S[d] + k_g[d] v_g;  acc_g += S[d] q_g[d]            g = 0 .. GROUP-1
+// so that neighbouring instructions belong to different accumulators; at the end of the group the four lanes'
+// partial sums are added (lane pairs first, then the pairs).  Every token's sum thus has one order that depends on
+// the head's size only: prompts, pieces of prompts and single tokens give the same bits (GROUP = 1, for steps in
+// which every sequence brings one token, walks the same order).
+#define GLA_SPLIT 4
+template <typename T, int DIMC, int GROUP>
+__global__ void __launch_bounds__(GLA_COLS)
+gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, int k_col, int v_col,
+                         const T* __restrict__ z, const float* __restrict__ bias, float inv_tau, float qscale,
+                         float* __restrict__ state, float* __restrict__ o, const int* __restrict__ seq_slot,
+                         const int* __restrict__ seq_start, int H, int dim, int vdim) {
+    constexpr int CH = DIMC / GLA_SPLIT;                                     // channels per lane
+    constexpr int BCOLS = GLA_COLS / GLA_SPLIT;                              // columns per block
+    __shared__ __align__(16) float stage[2][GROUP][3][DIMC];
+    __shared__ float stage_v[2][GROUP][BCOLS];
+    constexpr int PER = (GROUP * DIMC + GLA_COLS - 1) / GLA_COLS;            // staged elements per thread and array
+    constexpr int VPER = (GROUP * BCOLS + GLA_COLS - 1) / GLA_COLS;          // staged values per thread
+    pdl_trigger();
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int col = threadIdx.x / GLA_SPLIT, part = threadIdx.x % GLA_SPLIT;
+    const int j = blockIdx.x * BCOLS + col;
+    const bool mine = j < vdim;
+    const int t0 = seq_start[b], t1 = seq_start[b + 1];
+    const int slot = seq_slot[b];
+    float bs[PER];
+#pragma unroll
+    for (int e = 0; e < PER; e++) {
+        const int d = (threadIdx.x + e * GLA_COLS) % DIMC;
+        bs[e] = d < dim ? bias[h * dim + d] : 0.0f;
+    }
+    pdl_wait();
+    float* st = state + ((size_t)slot * H + h) * dim * vdim;
+    float S[CH];
+#pragma unroll
+    for (int i = 0; i < CH; i++) {
+        const int d = (i / 4) * 4 * GLA_SPLIT + 4 * part + (i & 3);
+        S[i] = (mine && d < dim) ? st[(size_t)d * vdim + j] : 0.0f;
+    }
+    // as they come from memory (widened only when they are stored into a buffer, so that nothing waits for a load
+    // before the group at hand has been computed)
+    T rz[PER], rk[PER], rq[PER], rv[VPER];
+    auto fetch = [&](int base) {              // the raw values of tokens base .. base + GROUP - 1 into registers
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const int idx = threadIdx.x + e * GLA_COLS;
+            const int g = idx / DIMC, d = idx % DIMC, t = base + g;
+            rz[e] = rk[e] = rq[e] = T(0.0f);
+            if (g < GROUP && t < t1 && d < dim) {
+                const T* row = proj + (size_t)t * ld;
+                rz[e] = z[((size_t)t * H + h) * dim + d];
+                rk[e] = row[k_col + h * dim + d];
+                rq[e] = row[q_col + h * dim + d];
+            }
+        }
+        // the values: thread i takes token i / BCOLS of the group, column i % BCOLS (and so on, GLA_COLS further)
+#pragma unroll
+        for (int e = 0; e < VPER; e++) {
+            const int idx = threadIdx.x + e * GLA_COLS;
+            const int g = idx / BCOLS, c = idx % BCOLS, jj = blockIdx.x * BCOLS + c;
+            rv[e] = T(0.0f);
+            if (g < GROUP && base + g < t1 && jj < vdim) rv[e] = proj[(size_t)(base + g) * ld + v_col + h * vdim + jj];
+        }
+    };
+    auto store = [&](int buf, int base) {     // ... and from there into a buffer
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const int idx = threadIdx.x + e * GLA_COLS;
+            const int g = idx / DIMC, d = idx % DIMC;
+            if (g < GROUP) {
+                // a token past the sequence's end: decay 1, key 0 (the state stays); a channel past dim: all zero
+                const bool live = base + g < t1;
+                stage[buf][g][0][d] = d < dim ? (live ? gla_decay(ld_f(&rz[e]) + bs[e], inv_tau) : 1.0f) : 0.0f;
+                stage[buf][g][1][d] = ld_f(&rk[e]);
+                stage[buf][g][2][d] = ld_f(&rq[e]) * qscale;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VPER; e++) {
+            const int idx = threadIdx.x + e * GLA_COLS;
+            if (idx < GROUP * BCOLS) stage_v[buf][idx / BCOLS][idx % BCOLS] = ld_f(&rv[e]);
+        }
+    };
+    fetch(t0);
+    store(0, t0);
+    __syncthreads();
+    int buf = 0;
+    for (int base = t0; base < t1; base += GROUP) {
+        const bool more = base + GROUP < t1;
+        if (more) fetch(base + GROUP);
+        float acc[GROUP], vv[GROUP];
+#pragma unroll
+        for (int g = 0; g < GROUP; g++) {
+            acc[g] = 0.0f;
+            vv[g] = stage_v[buf][g][col];
+        }
+#pragma unroll
+        for (int c = 0; c < CH / 4; c++) {
+#pragma unroll
+            for (int g = 0; g < GROUP; g++) {
+                const int at = (c * GLA_SPLIT + part) * 4;
+                const float4 a = *reinterpret_cast<const float4*>(&stage[buf][g][0][at]);
+                const float4 k = *reinterpret_cast<const float4*>(&stage[buf][g][1][at]);
+                const float4 q = *reinterpret_cast<const float4*>(&stage[buf][g][2][at]);
+                S[4 * c] = fmaf(a.x, S[4 * c], k.x * vv[g]);
+                acc[g] = fmaf(S[4 * c], q.x, acc[g]);
+                S[4 * c + 1] = fmaf(a.y, S[4 * c + 1], k.y * vv[g]);
+                acc[g] = fmaf(S[4 * c + 1], q.y, acc[g]);
+                S[4 * c + 2] = fmaf(a.z, S[4 * c + 2], k.z * vv[g]);
+                acc[g] = fmaf(S[4 * c + 2], q.z, acc[g]);
+                S[4 * c + 3] = fmaf(a.w, S[4 * c + 3], k.w * vv[g]);
+                acc[g] = fmaf(S[4 * c + 3], q.w, acc[g]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < GROUP; g++) {
+            acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
+            acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 2);
+        }
+        // all four lanes hold the sums: lane p writes tokens p, p + 4, ..
+#pragma unroll
+        for (int g = 0; g < GROUP; g++)
+            if (mine && (g % GLA_SPLIT) == part && base + g < t1) o[((size_t)(base + g) * H + h) * vdim + j] = acc[g];
+        if (more) store(buf ^ 1, base + GROUP);
+        __syncthreads();              // the next group is staged, and everyone is done with this one
+        buf ^= 1;
+    }
+    if (mine) {
+#pragma unroll
+        for (int i = 0; i < CH; i++) {
+            const int d = (i / 4) * 4 * GLA_SPLIT + 4 * part + (i & 3);
+            if (d < dim) st[(size_t)d * vdim + j] = S[i];
+        }
+    }
+}
+
+// Any number of key channels: the state tile [dim][GLA_TILE] lives in shared memory.
 template <typename T>
 __global__ void __launch_bounds__(GLA_TILE)
 gla_recurrent_kernel(const T* __restrict__ proj, long long ld, int q_col, int k_col, int v_col, const T* __restrict__ z,
@@ -67,10 +213,38 @@ gla_recurrent_kernel(const T* __restrict__ proj, long long ld, int q_col, int k_
 
 extern "C" int ri_gla_recurrent(const void* proj, long long ld, int q_col, int k_col, int v_col, const void* z,
                                 const float* bias, float tau, float qscale, float* state, float* o, const int* seq_slot,
-                                const int* seq_start, int seqs, int H, int dim, int vdim, int dtype, cudaStream_t stream) {
+                                const int* seq_start, int seqs, int H, int dim, int vdim, int single, int dtype,
+                                cudaStream_t stream) {
+    // single: every sequence brings one token (a smaller staging group; the same results)
     if (seqs == 0) return 0;
     RI_REQUIRE(seqs > 0 && H > 0 && dim > 0 && vdim > 0 && tau > 0.0f, "gla_recurrent: bad sizes");
     RI_REQUIRE(seqs <= 65535 && H <= 65535, "gla_recurrent: %d sequences, %d heads: too many for one launch", seqs, H);
+    RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "gla_recurrent: unknown dtype %d", dtype);
+    if (dim <= 128) {
+        const int threads = GLA_COLS;             // all of them stage the tokens, whatever the number of columns
+        const dim3 grid((vdim + GLA_COLS / GLA_SPLIT - 1) / (GLA_COLS / GLA_SPLIT), H, seqs);
+#define GLA_REG1(T, DIMC, GROUP)                                                                                           \
+        ri_launch_pdl(gla_recurrent_reg_kernel<T, DIMC, GROUP>, grid, dim3(threads), 0, stream, (const T*)proj, ld, q_col,  \
+                      k_col, v_col, (const T*)z, bias, 1.0f / tau, qscale, state, o, seq_slot, seq_start, H, dim, vdim)
+#define GLA_REG(T, DIMC)                                                                                                   \
+        do {                                                                                                               \
+            if (single) GLA_REG1(T, DIMC, 1);                                                                              \
+            else GLA_REG1(T, DIMC, 8);                                                                                     \
+        } while (0)
+#define GLA_BY_DIM(T)                                                                                                      \
+        do {                                                                                                               \
+            if (dim <= 32) GLA_REG(T, 32);                                                                                 \
+            else if (dim <= 64) GLA_REG(T, 64);                                                                            \
+            else GLA_REG(T, 128);                                                                                          \
+        } while (0)
+        if (dtype == RI_DTYPE_F32) GLA_BY_DIM(float);
+        else GLA_BY_DIM(__nv_bfloat16);
+#undef GLA_BY_DIM
+#undef GLA_REG
+#undef GLA_REG1
+        RI_CHECK_LAUNCH("gla_recurrent");
+        return 0;
+    }
     const size_t smem = ((size_t)dim * GLA_TILE + 6 * (size_t)dim) * sizeof(float);
     RI_REQUIRE(smem <= 200 * 1024, "gla_recurrent: %d key channels per head do not fit in shared memory", dim);
     const dim3 grid((vdim + GLA_TILE - 1) / GLA_TILE, H, seqs);
@@ -83,8 +257,7 @@ extern "C" int ri_gla_recurrent(const void* proj, long long ld, int q_col, int k
                       (const T*)z, bias, 1.0f / tau, qscale, state, o, seq_slot, seq_start, H, dim, vdim);                 \
     } while (0)
     if (dtype == RI_DTYPE_F32) GLA_GO(float);
-    else if (dtype == RI_DTYPE_BF16) GLA_GO(__nv_bfloat16);
-    else RI_FAIL(-1, "gla_recurrent: unknown dtype %d", dtype);
+    else GLA_GO(__nv_bfloat16);
 #undef GLA_GO
     RI_CHECK_LAUNCH("gla_recurrent");
     return 0;

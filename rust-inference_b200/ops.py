@@ -28,7 +28,7 @@ _SIGNATURES = {
     ("elementwise", "ri_gate_heads"): [_P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     ("streams", "ri_stream_norm"): [_P] * 8 + [_I, _I, _I, _F, _I, _I, _P],
     ("latent_attention", "ri_latent_prep"): [_P, _L, _I, _I] + [_P] * 8 + [_F, _P] + [_I] * 11 + [_P, _P],
-    ("gla", "ri_gla_recurrent"): [_P, _L, _I, _I, _I, _P, _P, _F, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    ("gla", "ri_gla_recurrent"): [_P, _L, _I, _I, _I, _P, _P, _F, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     ("gla", "ri_gla_head_norm_gate"): [_P, _P, _F, _P, _L, _P, _I, _I, _I, _I, _I, _P],
     ("linear_f32", "ri_linear_heads_f32"): [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _P],
     ("elementwise", "ri_rmsnorm"): [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _P, _I, _I, _P],
@@ -343,12 +343,13 @@ def latent_prep(proj: torch.Tensor, q_col: int, dkv_col: int, qa: torch.Tensor, 
 
 def gla_recurrent(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, bias: torch.Tensor, tau: float,
                   qscale: float, state: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, heads: int, dim: int,
-                  vdim: int) -> torch.Tensor:
+                  vdim: int, single: bool = False) -> torch.Tensor:
     """Gated linear attention over the step's new tokens.  Per (sequence, head) the state S [dim, vdim] (float32, in
     ``state`` [slots, H, dim, vdim], updated in place) goes S <- diag(a_t) S + k_t v_t^T with the decay
     a_t = sigmoid(z_t + bias)^(1/tau) per key channel, and o_t = S^T (q_t qscale).  q, k, v are columns of ``proj``
-    [tokens, N] from ``q_col``, ``k_col``, ``v_col`` (head after head); ``z`` [tokens, H*dim].  Returns o [tokens, H, vdim]
-    in float32."""
+    [tokens, N] from ``q_col``, ``k_col``, ``v_col`` (head after head); ``z`` [tokens, H*dim].  ``single``: every sequence
+    brings one token (the kernel then stages one token at a time; the results are the same bits).  Returns
+    o [tokens, H, vdim] in float32."""
     _need(proj, "proj")
     tokens, ld = proj.shape
     _need(z, "z", proj.dtype, (tokens, heads * dim))
@@ -364,7 +365,7 @@ def gla_recurrent(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: tor
     o = torch.empty((tokens, heads, vdim), dtype=torch.float32, device=proj.device)
     _call("gla", "ri_gla_recurrent", proj.data_ptr(), ld, int(q_col), int(k_col), int(v_col), z.data_ptr(), bias.data_ptr(),
           float(tau), float(qscale), state.data_ptr(), o.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seqs, heads,
-          dim, vdim, _code(proj.dtype), _stream())
+          dim, vdim, 1 if single and tokens == seqs else 0, _code(proj.dtype), _stream())
     return o
 
 

@@ -62,7 +62,7 @@ class GatedLinearAttention(Mixer):
             z = ops.linear(ops.linear(x, self.a1), self.a2)
         with section("gla recurrence"):
             o = ops.gla_recurrent(proj, self.q_col, self.k_col, self.v_col, z, self.bias, s.tau, s.dim ** -0.5, cache.state,
-                                  ctx.seq_slot, ctx.seq_start, H, s.dim, s.vdim)
+                                  ctx.seq_slot, ctx.seq_start, H, s.dim, s.vdim, single=ctx.decode_only)
         with section("gla norm/gate"):
             y = ops.head_norm_gate(o, self.gain, s.eps, proj[:, self.g_col:self.g_col + H * s.vdim], self.env.dtype, "silu")
         with section("gla o proj"):

@@ -93,7 +93,7 @@ def latent_prep(proj, q_col, dkv_col, qa, heads, dim, rot, rank, gain, eps, rope
     return torch.cat([qa.float(), qr], dim=-1).to(proj.dtype).contiguous()
 
 
-def gla_recurrent(proj, q_col, k_col, v_col, z, bias, tau, qscale, state, seq_slot, seq_start, heads, dim, vdim):
+def gla_recurrent(proj, q_col, k_col, v_col, z, bias, tau, qscale, state, seq_slot, seq_start, heads, dim, vdim, single=False):
     T = proj.shape[0]
     p = proj.float()
     q = p[:, q_col:q_col + heads * dim].view(T, heads, dim) * qscale

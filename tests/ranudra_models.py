@@ -156,10 +156,11 @@ def row_error(got, want):
 
 
 # float32: rounding alone (sums of a few hundred float32 terms over a dozen sublayers).  bfloat16: activations are
-# rounded to 8 bits between the parts of every sublayer, and these weights make attention sharp, so a single row may
-# be a tenth off (a wrong mechanism is off by about one); the mean over all rows is held much tighter.  What the
-# bfloat16 kernels compute is held to 1.2 % by the kernel tests.
-BOUND = {"float32": (2e-5, 1e-5), "bfloat16": (2.5e-1, 4e-2)}
+# rounded to 8 bits between the parts of every sublayer, and these weights make attention sharp and the layers deep
+# (a run of layers three times over), so single rows are a few tenths off where a rounding tips a sharp softmax; the
+# mean over all rows is held much tighter (a wrong mechanism moves every row by about one).  The same code runs both
+# dtypes apart from the kernels, and what the bfloat16 kernels compute is held to 1.2 % by the kernel tests.
+BOUND = {"float32": (2e-5, 1e-5), "bfloat16": (6e-1, 5e-2)}
 
 
 def assert_rows_close(rows, want_by_request, dtype, what=""):
@@ -170,4 +171,4 @@ def assert_rows_close(rows, want_by_request, dtype, what=""):
         assert err <= BOUND[dtype][0], f"{what}: request {rid} position {p}: error {err:.3e} exceeds {BOUND[dtype][0]:.1e}"
     mean = total / max(len(rows), 1)
     assert mean <= BOUND[dtype][1], f"{what}: mean error {mean:.3e} exceeds {BOUND[dtype][1]:.1e}"
-    return worst
+    return round(worst, 7), round(mean, 7)

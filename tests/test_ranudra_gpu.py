@@ -135,6 +135,12 @@ def test_gla_recurrence_and_state(H, dim, vdim, dtype):
     o2 = ops.gla_recurrent(rest[0], q_col, k_col, v_col, rest[1], _t(bias), tau, dim ** -0.5, state2, slots,
                            torch.tensor([0, 7, 10], dtype=torch.int32, device=DEV), H, dim, vdim)
     assert torch.equal(torch.cat([o1[:30], o2[:7], o1[30:], o2[7:]]), o) and torch.equal(state2, state)
+    # ... and token by token with the kernel's variant for steps of single tokens
+    state3 = torch.zeros_like(state)
+    one = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    outs = [ops.gla_recurrent(proj[t:t + 1].contiguous(), q_col, k_col, v_col, z[t:t + 1].contiguous(), _t(bias), tau,
+                              dim ** -0.5, state3, slots[:1], one, H, dim, vdim, single=True) for t in range(lens[0])]
+    assert torch.equal(torch.cat(outs), o[:lens[0]]) and torch.equal(state3[2], state[2])
     # norm over the value size, one gain for all heads, silu gate from columns of the projection
     y = ops.head_norm_gate(o, _t(gain), eps, proj[:, g_col:g_col + H * vdim], dtype, "silu")
     od = o.double().cpu().numpy()
