@@ -28,7 +28,7 @@ def _ids(text: str):
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="runner", description="Token-id generation with a Qwen3 checkpoint on one B200")
+    ap = argparse.ArgumentParser(prog="runner", description="Token-id generation with a checkpoint of a registered architecture on one B200")
     ap.add_argument("model_dir", help="folder with config.json and *.safetensors")
     ap.add_argument("-p", "--prompt", action="append", help="prompt as token ids; may be given several times")
     ap.add_argument("--prompt-file", help="file with one prompt (token ids) per line")
