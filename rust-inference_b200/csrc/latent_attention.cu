@@ -9,9 +9,9 @@
 // is what the value up-projection is applied to afterwards.  So attention runs as many query heads over ONE
 // key/value head of rank + rot elements whose values are the keys themselves.
 //
-// This kernel, one block per new token:
-//   * norms the latent, rotates the shared key part and appends the row to the token's page;
-//   * writes the query rows  qf[t, h] = [ qa[t, h] (rank), rot(q_turn[t, h]) (rot) ].
+// This kernel, one block per (new token, head) and one more per token for the cache row:
+//   * the row's block norms the latent, rotates the shared key part and appends the row to the token's page;
+//   * a head's block writes its query row  qf[t, h] = [ qa[t, h] (rank), rot(q_turn[t, h]) (rot) ].
 // Rotation: neighbouring elements (2i, 2i+1) are turned by the angle of position x frequency i; the
 // table [positions, rot/2, 2] holds cos and sin (with any factor on both already in it).
 // All arithmetic is float32; T (float or bfloat16) is the storage type.
@@ -31,7 +31,7 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, long long ld, int
                                    int num_pages, int write, int* __restrict__ err) {
     __shared__ float red[33];
     pdl_trigger();
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, h = blockIdx.y;              // h == H: the cache row
     const int pos = tok_pos[t];
     const int slot = seq_slot[tok_seq[t]];
     pdl_wait();
@@ -42,7 +42,8 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, long long ld, int
     const T* row = proj + (size_t)t * ld;
     const float* cs = table + (size_t)pos * rot;              // [rot/2][2]
     const int Dk = rank + rot;
-    if (write) {
+    if (h == H) {
+        if (!write) return;
         const int page = (pos / page_size) < mpps ? page_table[(size_t)slot * mpps + pos / page_size] : -1;
         float ss = 0.0f;
         for (int i = threadIdx.x; i < rank; i += blockDim.x) {
@@ -52,30 +53,27 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, long long ld, int
         const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)rank + eps);
         if (page < 0 || page >= num_pages) {
             if (threadIdx.x == 0) atomicExch(err, 2);
-        } else {
-            T* dst = pool + ((size_t)page * page_size + pos % page_size) * Dk;
-            for (int i = threadIdx.x; i < rank; i += blockDim.x) st_f(dst + i, ld_f(row + dkv_col + i) * inv * gain[i]);
-            for (int j = threadIdx.x; j < rot / 2; j += blockDim.x) {
-                const float u = ld_f(row + dkv_col + rank + 2 * j), v = ld_f(row + dkv_col + rank + 2 * j + 1);
-                const float c = cs[2 * j], s = cs[2 * j + 1];
-                st_f(dst + rank + 2 * j, u * c - v * s);
-                st_f(dst + rank + 2 * j + 1, v * c + u * s);
-            }
+            return;
         }
+        T* dst = pool + ((size_t)page * page_size + pos % page_size) * Dk;
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) st_f(dst + i, ld_f(row + dkv_col + i) * inv * gain[i]);
+        for (int j = threadIdx.x; j < rot / 2; j += blockDim.x) {
+            const float u = ld_f(row + dkv_col + rank + 2 * j), v = ld_f(row + dkv_col + rank + 2 * j + 1);
+            const float c = cs[2 * j], s = cs[2 * j + 1];
+            st_f(dst + rank + 2 * j, u * c - v * s);
+            st_f(dst + rank + 2 * j + 1, v * c + u * s);
+        }
+        return;
     }
-    for (int idx = threadIdx.x; idx < H * rank; idx += blockDim.x) {
-        const int h = idx / rank, i = idx - h * rank;
-        qf[((size_t)t * H + h) * Dk + i] = qa[(size_t)t * H * rank + idx];
-    }
-    const int half = rot / 2;
-    for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
-        const int h = idx / half, j = idx - h * half;
-        const T* qr = row + q_col + (size_t)h * (dim + rot) + dim;
+    T* dst = qf + ((size_t)t * H + h) * Dk;
+    const T* src = qa + ((size_t)t * H + h) * rank;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = src[i];
+    const T* qr = row + q_col + (size_t)h * (dim + rot) + dim;
+    for (int j = threadIdx.x; j < rot / 2; j += blockDim.x) {
         const float u = ld_f(qr + 2 * j), v = ld_f(qr + 2 * j + 1);
         const float c = cs[2 * j], s = cs[2 * j + 1];
-        T* dst = qf + ((size_t)t * H + h) * Dk + rank;
-        st_f(dst + 2 * j, u * c - v * s);
-        st_f(dst + 2 * j + 1, v * c + u * s);
+        st_f(dst + rank + 2 * j, u * c - v * s);
+        st_f(dst + rank + 2 * j + 1, v * c + u * s);
     }
 }
 
@@ -87,9 +85,10 @@ extern "C" int ri_latent_prep(const void* proj, long long ld, int q_col, int dkv
     if (tokens == 0) return 0;
     RI_REQUIRE(tokens > 0 && H > 0 && dim >= 0 && rank > 0 && rot >= 0 && rot % 2 == 0, "latent_prep: bad sizes");
     RI_REQUIRE(rot == 0 || table, "latent_prep: a rotated part needs the table of angles");
-    const int threads = 128;
+    RI_REQUIRE(H < 65535, "latent_prep: %d heads: too many for one launch", H);
+    const int threads = 64;
 #define LP_GO(T)                                                                                                             \
-    ri_launch_pdl(latent_prep_kernel<T>, dim3(tokens), dim3(threads), 0, stream, (const T*)proj, ld, q_col, dkv_col,         \
+    ri_launch_pdl(latent_prep_kernel<T>, dim3(tokens, H + 1), dim3(threads), 0, stream, (const T*)proj, ld, q_col, dkv_col,         \
                   (const T*)qa, (T*)qf, (T*)pool, page_table, tok_seq, tok_pos, seq_slot, gain, eps, table, table_rows, H,   \
                   dim, rot, rank, mpps, page_size, num_pages, write, err_flag)
     if (dtype == RI_DTYPE_F32) LP_GO(float);

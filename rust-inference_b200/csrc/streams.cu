@@ -87,6 +87,103 @@ stream_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const
     for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(op + i, (sn_row[i] - mean) * inv * gain[i]);
 }
 
+// The same for rows whose length is a multiple of 4 (and 16-byte aligned data): four neighbouring elements per
+// thread and trip, 16-byte loads and stores.  An element's own arithmetic is as above; the row's sums are taken
+// over other partial sums, so the two kernels may differ in the last bit (which one runs depends on the row
+// length and the addresses only, never on the batch).
+__device__ __forceinline__ float4 sn_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 sn_ld4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void sn_st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void sn_st4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const unsigned*>(&a);
+    u.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename T, int NS>
+__global__ void __launch_bounds__(512)
+stream_norm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ mix,
+                       const float* __restrict__ outw, const float* __restrict__ read, const int* __restrict__ rows,
+                       const float* __restrict__ gain, T* __restrict__ out, int dim, float eps, int kind, int write_back) {
+    extern __shared__ __align__(16) float sn_row[];                 // [dim]
+    __shared__ float red[33];
+    __shared__ float s_mix[NS * NS], s_out[NS], s_read[NS];
+    pdl_trigger();
+    for (int i = threadIdx.x; i < NS * NS; i += blockDim.x) s_mix[i] = mix ? mix[i] : (i / NS == i % NS ? 1.0f : 0.0f);
+    for (int i = threadIdx.x; i < NS; i += blockDim.x) {
+        s_out[i] = outw ? outw[i] : 1.0f;
+        s_read[i] = read ? read[i] : 1.0f;
+    }
+    const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+    pdl_wait();
+    __syncthreads();
+    float* rp = resid + r * NS * dim;
+    const T* dp = delta ? delta + r * dim : nullptr;
+    const int nvec = dim >> 2;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        float x[NS][4];
+#pragma unroll
+        for (int s = 0; s < NS; s++) {
+            const float4 v = sn_ld4(rp + (size_t)s * dim + 4 * i);
+            x[s][0] = v.x; x[s][1] = v.y; x[s][2] = v.z; x[s][3] = v.w;
+        }
+        float u[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (dp) {
+            const float4 yv = sn_ld4(dp + 4 * i);
+            const float y[4] = {yv.x, yv.y, yv.z, yv.w};
+#pragma unroll
+            for (int t = 0; t < NS; t++) {
+                float a[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    a[e] = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < NS; s++) a[e] = fmaf(s_mix[s * NS + t], x[s][e], a[e]);
+                    a[e] = fmaf(s_out[t], y[e], a[e]);
+                    u[e] = fmaf(s_read[t], a[e], u[e]);
+                }
+                if (write_back) sn_st4(rp + (size_t)t * dim + 4 * i, make_float4(a[0], a[1], a[2], a[3]));
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < NS; t++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) u[e] = fmaf(s_read[t], x[t][e], u[e]);
+        }
+        *reinterpret_cast<float4*>(sn_row + 4 * i) = make_float4(u[0], u[1], u[2], u[3]);
+        if (kind == SN_KIND_LAYERNORM) sum += (u[0] + u[1]) + (u[2] + u[3]);
+        else sum += (u[0] * u[0] + u[1] * u[1]) + (u[2] * u[2] + u[3] * u[3]);
+    }
+    float total = block_sum(sum, red);
+    float mean = 0.0f, inv;
+    if (kind == SN_KIND_LAYERNORM) {
+        mean = total / (float)dim;
+        float sq = 0.0f;
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(sn_row + 4 * i);
+            const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
+            sq += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+        }
+        inv = 1.0f / sqrtf(block_sum(sq, red) / (float)dim + eps);
+    } else {
+        inv = 1.0f / sqrtf(total / (float)dim + eps);
+    }
+    T* op = out + (size_t)blockIdx.x * dim;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        const float4 v = *reinterpret_cast<const float4*>(sn_row + 4 * i);
+        const float4 g = sn_ld4(gain + 4 * i);
+        sn_st4(op + 4 * i, make_float4((v.x - mean) * inv * g.x, (v.y - mean) * inv * g.y, (v.z - mean) * inv * g.z,
+                                       (v.w - mean) * inv * g.w));
+    }
+}
+
 extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix, const float* outw, const float* read,
                               const int* rows, const float* gain, void* out, int n_rows, int streams, int dim, float eps,
                               int kind, int dtype, cudaStream_t stream) {
@@ -96,12 +193,36 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
     RI_REQUIRE(kind == SN_KIND_LAYERNORM || kind == SN_KIND_RMSNORM, "stream_norm: unknown norm %d", kind);
     const size_t smem = (size_t)dim * sizeof(float);
     RI_REQUIRE(smem <= 200 * 1024, "stream_norm: a row of %d elements does not fit in shared memory (limit 51200)", dim);
-    const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+    int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
     const int write_back = rows ? 0 : 1;
+    // rows of whole float4s at aligned addresses, up to 8 streams: the vector kernel (many rows: smaller blocks,
+    // several of which share an SM)
+    const uintptr_t al = (uintptr_t)resid | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)out;
+    const int unit = dtype == RI_DTYPE_F32 ? 15 : 7;
+    const bool vec = dim % 4 == 0 && streams <= 8 && (((uintptr_t)resid | (uintptr_t)gain) & 15) == 0 &&
+                     (((uintptr_t)delta | (uintptr_t)out) & unit) == 0;
+    (void)al;
+    if (vec) {
+        const int nvec = dim / 4;
+        threads = n_rows >= 256 ? 256 : (nvec >= 512 ? 512 : ((nvec + 31) / 32) * 32);
+        threads = nvec < threads ? ((nvec + 31) / 32) * 32 : threads;
+    }
     RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "stream_norm: unknown dtype %d", dtype);
     cudaError_t e = cudaSuccess;
+#define SN_VEC(T, NS)                                                                                                    \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024)                                                                                            \
+            e = cudaFuncSetAttribute(stream_norm_vec_kernel<T, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) RI_FAIL((int)e, "stream_norm: %s", cudaGetErrorString(e));                                 \
+        ri_launch_pdl(stream_norm_vec_kernel<T, NS>, dim3(n_rows), dim3(threads), smem, stream, resid, (const T*)delta,   \
+                      mix, outw, read, rows, gain, (T*)out, dim, eps, kind, write_back);                                 \
+    } while (0)
 #define SN_GO(T, NS)                                                                                                     \
     do {                                                                                                                 \
+        if (vec && NS > 0) {                                                                                             \
+            SN_VEC(T, (NS > 0 ? NS : 1));                                                                                \
+            break;                                                                                                       \
+        }                                                                                                                \
         if (smem > 48 * 1024)                                                                                            \
             e = cudaFuncSetAttribute(stream_norm_kernel<T, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         if (e != cudaSuccess) RI_FAIL((int)e, "stream_norm: %s", cudaGetErrorString(e));                                 \
@@ -124,6 +245,7 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
     else SN_BY_STREAMS(__nv_bfloat16)
 #undef SN_BY_STREAMS
 #undef SN_GO
+#undef SN_VEC
     RI_CHECK_LAUNCH("stream_norm");
     return 0;
 }
