@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "mma_helpers.cuh"
 #include <float.h>
+#include <stddef.h>
 
 #ifndef RI_HEAD_DIM
 #define RI_HEAD_DIM 128
@@ -39,7 +40,7 @@ struct __align__(16) PrefillSmem {
 // keys [kb*64, kb*64+63] of one kv head into buffer `buf`: two pages, 16 bytes per copy
 __device__ __forceinline__ void load_kv_block(PrefillSmem& sm, int buf, int kb, const bf16* __restrict__ k_pool,
                                               const bf16* __restrict__ v_pool, const int* __restrict__ table, int kvh,
-                                              int KV, int num_pages, int len, int key_lo, int* err) {
+                                              int KV, int num_pages, int len, int key_lo, int* err, bool with_v = true) {
     constexpr int VEC = PF_DH / 8;
     for (int i = threadIdx.x; i < PF_BN * VEC; i += blockDim.x) {
         int r = i / VEC, c = (i % VEC) * 8;
@@ -58,7 +59,7 @@ __device__ __forceinline__ void load_kv_block(PrefillSmem& sm, int buf, int kb, 
             }
         }
         cp_async16(&sm.k[buf][r][c], k_pool + off, ok);
-        cp_async16(&sm.v[buf][r][c], v_pool + off, ok);
+        if (with_v) cp_async16(&sm.v[buf][r][c], v_pool + off, ok);
     }
 }
 
@@ -66,8 +67,11 @@ __global__ void __launch_bounds__(32 * PF_WARPS)
 attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                          bf16* __restrict__ out, const int* __restrict__ page_table, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_len, int H, int KV, int mpps,
-                         int num_pages, float scale_log2, int window, const float* __restrict__ sink,
-                         int* __restrict__ err) {
+                         int num_pages, float scale_log2, int window, const float* __restrict__ sink, int shared_kv,
+                         int v_dims, int* __restrict__ err) {
+    // shared_kv: the values are the keys (one pool given as both): the key tiles serve as value tiles, nothing is
+    // loaded twice and the block needs a third less shared memory.  v_dims: the leading value elements that are
+    // wanted (a multiple of 16; the rest of an output row is written as zeros).
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PrefillSmem& sm = *reinterpret_cast<PrefillSmem*>(smem_raw);
     const int b = blockIdx.z, h = blockIdx.y;
@@ -93,7 +97,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
         const bf16* src = q + ((size_t)(t_begin + r_base + (ok ? r : 0)) * H + h) * PF_DH + c;
         cp_async16(&sm.q[r][c], src, ok);
     }
-    load_kv_block(sm, 0, kb_lo, k_pool, v_pool, table, kvh, KV, num_pages, len, key_lo, err);
+    load_kv_block(sm, 0, kb_lo, k_pool, v_pool, table, kvh, KV, num_pages, len, key_lo, err, !shared_kv);
     cp_async_commit();
 
     float o[PF_DH / 8][4];
@@ -106,7 +110,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 
     for (int kb = kb_lo; kb <= kb_hi; kb++) {
         const int buf = (kb - kb_lo) & 1;
-        if (kb < kb_hi) load_kv_block(sm, buf ^ 1, kb + 1, k_pool, v_pool, table, kvh, KV, num_pages, len, key_lo, err);
+        if (kb < kb_hi) load_kv_block(sm, buf ^ 1, kb + 1, k_pool, v_pool, table, kvh, KV, num_pages, len, key_lo, err, !shared_kv);
         cp_async_commit();
         cp_async_wait<1>();              // everything but the block just asked for has arrived
         __syncthreads();
@@ -170,15 +174,17 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                 l[e >> 1] += p;
             }
         // ---- O += P V ---------------------------------------------------------------------------------
+        const bf16 (*vt)[PF_PITCH] = shared_kv ? sm.k[buf] : sm.v[buf];
 #pragma unroll
         for (int kk = 0; kk < PF_BN / 16; kk++) {
             unsigned a0 = pack_bf16(s[kk * 2][0], s[kk * 2][1]), a1 = pack_bf16(s[kk * 2][2], s[kk * 2][3]);
             unsigned a2 = pack_bf16(s[kk * 2 + 1][0], s[kk * 2 + 1][1]), a3 = pack_bf16(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
 #pragma unroll
             for (int dp = 0; dp < PF_DH / 16; dp++) {
+                if (dp * 16 >= v_dims) continue;
                 unsigned b0, b1, b2, b3;
                 ldmatrix_x4_trans(b0, b1, b2, b3,
-                                  &sm.v[buf][kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][dp * 16 + (lane >> 4) * 8]);
+                                  &vt[kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][dp * 16 + (lane >> 4) * 8]);
                 mma_bf16(o[dp * 2], a0, a1, a2, a3, b0, b1);
                 mma_bf16(o[dp * 2 + 1], a0, a1, a2, a3, b2, b3);
             }
@@ -217,24 +223,30 @@ extern "C" int ri_attention_prefill(const void* q, const void* k_pool, const voi
                                     const int* page_table, const int* seq_slot, const int* seq_start,
                                     const int* seq_len, int seqs, int max_new, int H, int KV, int Dh, int mpps,
                                     int page_size, int num_pages, float scale, int window, const float* sink,
-                                    int* err_flag, cudaStream_t stream) {
+                                    int v_dims, int* err_flag, cudaStream_t stream) {
     if (seqs == 0 || max_new == 0) return 0;
     RI_REQUIRE(Dh == PF_DH, "attention_prefill: built for head_dim %d, called with %d", PF_DH, Dh);
     RI_REQUIRE(page_size == PF_PAGE, "attention_prefill: pages of %d tokens, this kernel needs %d", page_size, PF_PAGE);
     RI_REQUIRE(H > 0 && KV > 0 && H % KV == 0, "attention_prefill: %d heads over %d kv heads", H, KV);
     RI_REQUIRE(seqs <= 65535 && H <= 65535, "attention_prefill: bad grid");
     RI_REQUIRE(window >= 0, "attention_prefill: negative window");
-    size_t smem = sizeof(PrefillSmem);
+    // v_dims: how many leading value elements are wanted (0: all); values that are the keys (v_pool == k_pool) are
+    // read from the key tiles
+    const int shared_kv = v_pool == k_pool ? 1 : 0;
+    if (v_dims <= 0 || v_dims > PF_DH) v_dims = PF_DH;
+    v_dims = (v_dims + 15) / 16 * 16;
+    size_t smem = shared_kv ? offsetof(PrefillSmem, v) : sizeof(PrefillSmem);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)sizeof(PrefillSmem));
         if (e != cudaSuccess) RI_FAIL((int)e, "attention_prefill: %s", cudaGetErrorString(e));
         configured = true;
     }
     dim3 grid((max_new + PF_BM - 1) / PF_BM, H, seqs);
     attention_prefill_kernel<<<grid, 32 * PF_WARPS, smem, stream>>>(
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, page_table, seq_slot, seq_start, seq_len,
-        H, KV, mpps, num_pages, scale * 1.4426950408889634f, window, sink, err_flag);
+        H, KV, mpps, num_pages, scale * 1.4426950408889634f, window, sink, shared_kv, v_dims, err_flag);
     RI_CHECK_LAUNCH("attention_prefill");
     return 0;
 }

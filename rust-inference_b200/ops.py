@@ -45,7 +45,7 @@ _SIGNATURES = {
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _P],
-    ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P, _P],
+    ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _I, _P, _P],
 }
 DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
 MAX_FAST_HEAD_DIM = 256
@@ -676,10 +676,12 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
 
 def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                       seq_slot: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_new: int,
-                      scale: float, window: int, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      scale: float, window: int, sink: Optional[torch.Tensor] = None, v_dims: int = 0) -> torch.Tensor:
     """Attention of the step's new tokens (q [tokens, H, Dh], bfloat16, sequences back
     to back as ``seq_start`` says) over the paged cache, which already holds their keys
-    and values; ``max_new`` is the most tokens one sequence brings."""
+    and values; ``max_new`` is the most tokens one sequence brings.  ``v_pool`` may be ``k_pool``
+    itself (values that are the keys): the mma.sync kernel then reads each tile once; ``v_dims`` > 0
+    says that only that many leading elements of the result are wanted (the rest may be zeros)."""
     _need(q, "q", torch.bfloat16)
     tokens, H, Dh = q.shape
     pages, KV, page_size, dh = k_pool.shape
@@ -705,7 +707,7 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     _call("attention_prefill", "ri_attention_prefill", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
           seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
-          _sink(sink, H), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+          _sink(sink, H), int(v_dims), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
     return out
 
 

@@ -109,7 +109,7 @@ class LatentAttention(Mixer):
                                            ctx.len_bucket, sink=self.sink)
             elif fast:
                 lat = ops.attention_prefill(qf, pool, pool, cache.page_table, ctx.seq_slot, ctx.seq_start, ctx.seq_len,
-                                            ctx.max_new, s.scale, s.window, sink=self.sink)
+                                            ctx.max_new, s.scale, s.window, sink=self.sink, v_dims=s.kv_rank)
             else:
                 lat = ops.attention(qf, pool, pool, cache.page_table, ctx.seq_slot, ctx.seq_start, ctx.seq_len, ctx.max_new,
                                     s.scale, s.window, sink=self.sink)
