@@ -18,7 +18,7 @@
 #include "common.cuh"
 
 #define GLA_TILE 64
-#define GLA_COLS 128            // threads per block of the register kernel
+#define GLA_COLS 512            // threads per block of the register kernel
 
 __device__ __forceinline__ float gla_decay(float z, float inv_tau) {
     // log(sigmoid(z)) = min(z, 0) - log1p(exp(-|z|))
@@ -26,35 +26,50 @@ __device__ __forceinline__ float gla_decay(float z, float inv_tau) {
     return expf(ls * inv_tau);
 }
 
-// The kernel for heads of up to 128 key channels.  Four neighbouring lanes share one value column of the state: each
-// keeps a quarter of the column's key channels in registers (DIMC / 4 of them, DIMC the head's key channels rounded
-// up to 32, 64 or 128; lane p of the four has channels 16 c + 4 p .. + 3 for c = 0, 1, ..; channels past `dim` hold
-// zeros and stay zero), so a block of 128 threads owns 32 columns.  The block stages the decay, key and scaled query
-// of GROUP tokens in shared memory (two buffers): the loads of the next group are on their way while the current
-// group is computed, and the decay's exponentials are taken when a group is stored.  A group that the sequence does
-// not fill is padded with tokens of decay 1 and key 0, which leave the state as it is, bit for bit.  A lane walks
-// its channels in the outer loop and the group's tokens in the inner one,
+// The kernel for heads of up to 128 key channels.  A block of 512 threads owns 32 value columns of the state, and
+// sixteen threads share a column: each keeps a sixteenth of the column's key channels in registers (DIMC / 16 of
+// them, DIMC the head's key channels rounded up to 64 or 128; channels past `dim` hold zeros and stay zero).  The
+// sixteen are four neighbouring lanes in each of four warps (part p = 4 (warp % 4) + lane % 4 has channels
+// 64 c + 4 p .. + 3 for c = 0, 1, ..; warps 4 i .. 4 i + 3 own columns 8 i .. 8 i + 7), so that a warp's loads and
+// stores of the state cover 8 neighbouring columns, and what the block stages per token serves 32 columns.
+// Many small threads instead of few large ones: the recurrence has little to do in parallel (heads x columns), and
+// this way a prompt of one sequence still puts some warps on every SM.
+// The block stages the decay, key and scaled query of GROUP tokens in shared memory (two buffers): the loads of the
+// next group are on their way while the current group is computed, and the decay's exponentials are taken when a
+// group is stored.  A group that the sequence does not fill is padded with tokens of decay 1 and key 0, which leave
+// the state as it is, bit for bit.  A thread walks its channels in the outer loop and the group's tokens in the
+// inner one,
 //     S[d] = a_g[d] S[d] + k_g[d] v_g;  acc_g += S[d] q_g[d]            g = 0 .. GROUP-1
-// so that neighbouring instructions belong to different accumulators; at the end of the group the four lanes'
-// partial sums are added (lane pairs first, then the pairs).  Every token's sum thus has one order that depends on
-// the head's size only: prompts, pieces of prompts and single tokens give the same bits (GROUP = 1, for steps in
-// which every sequence brings one token, walks the same order).
-#define GLA_SPLIT 4
+// so that neighbouring instructions belong to different accumulators; at the end of the group the partial sums are
+// added: the four lanes of a warp by shuffles (pairs first, then the pairs), the four warps through shared memory in
+// warp order.  Every token's sum thus has one order that depends on the head's size only: prompts, pieces of
+// prompts and single tokens give the same bits (GROUP = 1, for steps in which every sequence brings one token,
+// walks the same order).
+#define GLA_SPLIT 4             // lanes of a warp that share a column
+#define GLA_WARPS 4             // ... and warps
+#define GLA_BCOLS (GLA_COLS / GLA_SPLIT / GLA_WARPS)
 template <typename T, int DIMC, int GROUP>
 __global__ void __launch_bounds__(GLA_COLS)
 gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, int k_col, int v_col,
                          const T* __restrict__ z, const float* __restrict__ bias, float inv_tau, float qscale,
                          float* __restrict__ state, float* __restrict__ o, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, int H, int dim, int vdim) {
-    constexpr int CH = DIMC / GLA_SPLIT;                                     // channels per lane
-    constexpr int BCOLS = GLA_COLS / GLA_SPLIT;                              // columns per block
-    __shared__ __align__(16) float stage[2][GROUP][3][DIMC];
-    __shared__ float stage_v[2][GROUP][BCOLS];
+    constexpr int PARTS = GLA_SPLIT * GLA_WARPS;
+    constexpr int CH = DIMC / PARTS;                                         // channels per thread
+    constexpr int BCOLS = GLA_BCOLS;                                         // columns per block
+    static_assert(CH % 4 == 0 && GLA_COLS % (32 * GLA_WARPS) == 0, "whole float4s per thread; sets of four warps");
+    extern __shared__ __align__(16) float gla_dyn[];
+    float (*stage)[GROUP][3][DIMC] = reinterpret_cast<float (*)[GROUP][3][DIMC]>(gla_dyn);                 // [2]
+    float (*stage_v)[GROUP][BCOLS] = reinterpret_cast<float (*)[GROUP][BCOLS]>(gla_dyn + 2 * GROUP * 3 * DIMC);   // [2]
+    float (*partial)[GROUP][BCOLS][GLA_WARPS] =
+        reinterpret_cast<float (*)[GROUP][BCOLS][GLA_WARPS]>(gla_dyn + 2 * GROUP * 3 * DIMC + 2 * GROUP * BCOLS);  // [2]
     constexpr int PER = (GROUP * DIMC + GLA_COLS - 1) / GLA_COLS;            // staged elements per thread and array
     constexpr int VPER = (GROUP * BCOLS + GLA_COLS - 1) / GLA_COLS;          // staged values per thread
     pdl_trigger();
     const int b = blockIdx.z, h = blockIdx.y;
-    const int col = threadIdx.x / GLA_SPLIT, part = threadIdx.x % GLA_SPLIT;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wpart = warp % GLA_WARPS;                                      // this warp's share of the channels
+    const int col = (warp / GLA_WARPS) * (32 / GLA_SPLIT) + lane / GLA_SPLIT, part = wpart * GLA_SPLIT + lane % GLA_SPLIT;
     const int j = blockIdx.x * BCOLS + col;
     const bool mine = j < vdim;
     const int t0 = seq_start[b], t1 = seq_start[b + 1];
@@ -70,7 +85,7 @@ gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, in
     float S[CH];
 #pragma unroll
     for (int i = 0; i < CH; i++) {
-        const int d = (i / 4) * 4 * GLA_SPLIT + 4 * part + (i & 3);
+        const int d = (i / 4) * 4 * PARTS + 4 * part + (i & 3);
         S[i] = (mine && d < dim) ? st[(size_t)d * vdim + j] : 0.0f;
     }
     // as they come from memory (widened only when they are stored into a buffer, so that nothing waits for a load
@@ -93,7 +108,7 @@ gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, in
 #pragma unroll
         for (int e = 0; e < VPER; e++) {
             const int idx = threadIdx.x + e * GLA_COLS;
-            const int g = idx / BCOLS, c = idx % BCOLS, jj = blockIdx.x * BCOLS + c;
+            const int g = idx / BCOLS, jj = blockIdx.x * BCOLS + idx % BCOLS;
             rv[e] = T(0.0f);
             if (g < GROUP && base + g < t1 && jj < vdim) rv[e] = proj[(size_t)(base + g) * ld + v_col + h * vdim + jj];
         }
@@ -117,6 +132,19 @@ gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, in
             if (idx < GROUP * BCOLS) stage_v[buf][idx / BCOLS][idx % BCOLS] = ld_f(&rv[e]);
         }
     };
+    auto reduce = [&](int buf, int base) {    // a group's outputs: the four warps' sums in warp order
+#pragma unroll
+        for (int e = 0; e < VPER; e++) {
+            const int idx = threadIdx.x + e * GLA_COLS;
+            if (idx < GROUP * BCOLS) {
+                const int g = idx / BCOLS, c = idx % BCOLS, jj = blockIdx.x * BCOLS + c;
+                float acc = partial[buf][g][c][0];
+#pragma unroll
+                for (int w = 1; w < GLA_WARPS; w++) acc += partial[buf][g][c][w];
+                if (jj < vdim && base + g < t1) o[((size_t)(base + g) * H + h) * vdim + jj] = acc;
+            }
+        }
+    };
     fetch(t0);
     store(0, t0);
     __syncthreads();
@@ -134,7 +162,7 @@ gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, in
         for (int c = 0; c < CH / 4; c++) {
 #pragma unroll
             for (int g = 0; g < GROUP; g++) {
-                const int at = (c * GLA_SPLIT + part) * 4;
+                const int at = (c * PARTS + part) * 4;
                 const float4 a = *reinterpret_cast<const float4*>(&stage[buf][g][0][at]);
                 const float4 k = *reinterpret_cast<const float4*>(&stage[buf][g][1][at]);
                 const float4 q = *reinterpret_cast<const float4*>(&stage[buf][g][2][at]);
@@ -152,19 +180,17 @@ gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, in
         for (int g = 0; g < GROUP; g++) {
             acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
             acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 2);
+            if (lane % GLA_SPLIT == 0) partial[buf][g][col][wpart] = acc[g];
         }
-        // all four lanes hold the sums: lane p writes tokens p, p + 4, ..
-#pragma unroll
-        for (int g = 0; g < GROUP; g++)
-            if (mine && (g % GLA_SPLIT) == part && base + g < t1) o[((size_t)(base + g) * H + h) * vdim + j] = acc[g];
         if (more) store(buf ^ 1, base + GROUP);
-        __syncthreads();              // the next group is staged, and everyone is done with this one
+        __syncthreads();              // the next group is staged, this one's partial sums are written
+        reduce(buf, base);            // (the next group writes the other buffer of partial sums)
         buf ^= 1;
     }
     if (mine) {
 #pragma unroll
         for (int i = 0; i < CH; i++) {
-            const int d = (i / 4) * 4 * GLA_SPLIT + 4 * part + (i & 3);
+            const int d = (i / 4) * 4 * PARTS + 4 * part + (i & 3);
             if (d < dim) st[(size_t)d * vdim + j] = S[i];
         }
     }
@@ -222,19 +248,27 @@ extern "C" int ri_gla_recurrent(const void* proj, long long ld, int q_col, int k
     RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "gla_recurrent: unknown dtype %d", dtype);
     if (dim <= 128) {
         const int threads = GLA_COLS;             // all of them stage the tokens, whatever the number of columns
-        const dim3 grid((vdim + GLA_COLS / GLA_SPLIT - 1) / (GLA_COLS / GLA_SPLIT), H, seqs);
+        const dim3 grid((vdim + GLA_BCOLS - 1) / GLA_BCOLS, H, seqs);
 #define GLA_REG1(T, DIMC, GROUP)                                                                                           \
-        ri_launch_pdl(gla_recurrent_reg_kernel<T, DIMC, GROUP>, grid, dim3(threads), 0, stream, (const T*)proj, ld, q_col,  \
-                      k_col, v_col, (const T*)z, bias, 1.0f / tau, qscale, state, o, seq_slot, seq_start, H, dim, vdim)
+        do {                                                                                                               \
+            const size_t sm = (size_t)(2 * GROUP * 3 * DIMC + 2 * GROUP * GLA_BCOLS * (1 + GLA_WARPS)) * sizeof(float);    \
+            cudaError_t e = sm > 48 * 1024 ? cudaFuncSetAttribute(gla_recurrent_reg_kernel<T, DIMC, GROUP>,                \
+                                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)   \
+                                           : cudaSuccess;                                                                  \
+            if (e != cudaSuccess) RI_FAIL((int)e, "gla_recurrent: %s", cudaGetErrorString(e));                             \
+            ri_launch_pdl(gla_recurrent_reg_kernel<T, DIMC, GROUP>, grid, dim3(threads), sm, stream, (const T*)proj, ld,   \
+                          q_col, k_col, v_col, (const T*)z, bias, 1.0f / tau, qscale, state, o, seq_slot, seq_start, H,    \
+                          dim, vdim);                                                                                      \
+        } while (0)
+    // tokens staged together: many, so that a trip to memory is paid once per 16 tokens
 #define GLA_REG(T, DIMC)                                                                                                   \
         do {                                                                                                               \
             if (single) GLA_REG1(T, DIMC, 1);                                                                              \
-            else GLA_REG1(T, DIMC, 8);                                                                                     \
+            else GLA_REG1(T, DIMC, 16);                                                                 \
         } while (0)
 #define GLA_BY_DIM(T)                                                                                                      \
         do {                                                                                                               \
-            if (dim <= 32) GLA_REG(T, 32);                                                                                 \
-            else if (dim <= 64) GLA_REG(T, 64);                                                                            \
+            if (dim <= 64) GLA_REG(T, 64);                                                                                 \
             else GLA_REG(T, 128);                                                                                          \
         } while (0)
         if (dtype == RI_DTYPE_F32) GLA_BY_DIM(float);
