@@ -303,6 +303,7 @@ def run_design(a) -> int:
     windows = []
     out = {}
     for label, cfg in (("ranudra", ranudra_config(z)), ("qwen3", qwen3_like(z))):
+        t_model = time.time()
         model = Model.from_random(cfg, seed=1, dtype="bfloat16", device=dev)
         V = model.spec.vocab_size
         engine = Engine(model, max_tokens=B * ctx + T + 64, max_seqs=B + 1, max_seq_len=max(ctx, T))
@@ -376,6 +377,7 @@ def run_design(a) -> int:
             "decode_launches": launches // K, "graph_replays": engine.graph_replays,
             "decode_sections_us": dec_sections, "prefill_sections_us": pre_sections,
         }
+        windows.append((t_model, time.time()))         # the clocks of the whole measurement of this model
         del engine, model
         torch.cuda.empty_cache()
     clocks.stop()

@@ -9,7 +9,8 @@
 // is what the value up-projection is applied to afterwards.  So attention runs as many query heads over ONE
 // key/value head of rank + rot elements whose values are the keys themselves.
 //
-// This kernel, one block per (new token, head) and one more per token for the cache row:
+// This kernel, one block per (new token, head) and one more per token for the cache row (a prompt's many tokens:
+// one block for all heads of a token):
 //   * the row's block norms the latent, rotates the shared key part and appends the row to the token's page;
 //   * a head's block writes its query row  qf[t, h] = [ qa[t, h] (rank), rot(q_turn[t, h]) (rot) ].
 // Rotation: neighbouring elements (2i, 2i+1) are turned by the angle of position x frequency i; the
@@ -28,10 +29,12 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, long long ld, int
                                    const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
                                    const float* __restrict__ gain, float eps, const float* __restrict__ table,
                                    int table_rows, int H, int dim, int rot, int rank, int mpps, int page_size,
-                                   int num_pages, int write, int* __restrict__ err) {
+                                   int num_pages, int write, int heads_per_block, int* __restrict__ err) {
     __shared__ float red[33];
     pdl_trigger();
-    const int t = blockIdx.x, h = blockIdx.y;              // h == H: the cache row
+    const int t = blockIdx.x;
+    const int h0 = blockIdx.y * heads_per_block;           // h0 >= H: the cache row
+    const int h = h0 >= H ? H : h0;
     const int pos = tok_pos[t];
     const int slot = seq_slot[tok_seq[t]];
     pdl_wait();
@@ -65,15 +68,19 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, long long ld, int
         }
         return;
     }
-    T* dst = qf + ((size_t)t * H + h) * Dk;
-    const T* src = qa + ((size_t)t * H + h) * rank;
-    for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = src[i];
-    const T* qr = row + q_col + (size_t)h * (dim + rot) + dim;
-    for (int j = threadIdx.x; j < rot / 2; j += blockDim.x) {
+    const int h1 = min(H, h0 + heads_per_block), half = rot / 2;
+    for (int idx = threadIdx.x; idx < (h1 - h0) * rank; idx += blockDim.x) {
+        const int hh = h0 + idx / rank, i = idx % rank;
+        qf[((size_t)t * H + hh) * Dk + i] = qa[((size_t)t * H + hh) * rank + i];
+    }
+    for (int idx = threadIdx.x; idx < (h1 - h0) * half; idx += blockDim.x) {
+        const int hh = h0 + idx / half, j = idx % half;
+        const T* qr = row + q_col + (size_t)hh * (dim + rot) + dim;
         const float u = ld_f(qr + 2 * j), v = ld_f(qr + 2 * j + 1);
         const float c = cs[2 * j], s = cs[2 * j + 1];
-        st_f(dst + rank + 2 * j, u * c - v * s);
-        st_f(dst + rank + 2 * j + 1, v * c + u * s);
+        T* dst = qf + ((size_t)t * H + hh) * Dk + rank;
+        st_f(dst + 2 * j, u * c - v * s);
+        st_f(dst + 2 * j + 1, v * c + u * s);
     }
 }
 
@@ -86,11 +93,13 @@ extern "C" int ri_latent_prep(const void* proj, long long ld, int q_col, int dkv
     RI_REQUIRE(tokens > 0 && H > 0 && dim >= 0 && rank > 0 && rot >= 0 && rot % 2 == 0, "latent_prep: bad sizes");
     RI_REQUIRE(rot == 0 || table, "latent_prep: a rotated part needs the table of angles");
     RI_REQUIRE(H < 65535, "latent_prep: %d heads: too many for one launch", H);
-    const int threads = 64;
+    // few tokens: a block per head, so that the step's handful of rows is spread over the SMs; many: a block per token
+    const int hpb = tokens >= 256 ? H : 1;
+    const int threads = hpb == 1 ? 64 : 128;
 #define LP_GO(T)                                                                                                             \
-    ri_launch_pdl(latent_prep_kernel<T>, dim3(tokens, H + 1), dim3(threads), 0, stream, (const T*)proj, ld, q_col, dkv_col,         \
-                  (const T*)qa, (T*)qf, (T*)pool, page_table, tok_seq, tok_pos, seq_slot, gain, eps, table, table_rows, H,   \
-                  dim, rot, rank, mpps, page_size, num_pages, write, err_flag)
+    ri_launch_pdl(latent_prep_kernel<T>, dim3(tokens, (H + hpb - 1) / hpb + 1), dim3(threads), 0, stream, (const T*)proj, ld, \
+                  q_col, dkv_col, (const T*)qa, (T*)qf, (T*)pool, page_table, tok_seq, tok_pos, seq_slot, gain, eps, table,  \
+                  table_rows, H, dim, rot, rank, mpps, page_size, num_pages, write, hpb, err_flag)
     if (dtype == RI_DTYPE_F32) LP_GO(float);
     else if (dtype == RI_DTYPE_BF16) LP_GO(__nv_bfloat16);
     else RI_FAIL(-1, "latent_prep: unknown dtype %d", dtype);
