@@ -95,7 +95,7 @@ extern "C" int ri_latent_prep(const void* proj, long long ld, int q_col, int dkv
     RI_REQUIRE(H < 65535, "latent_prep: %d heads: too many for one launch", H);
     // few tokens: a block per head, so that the step's handful of rows is spread over the SMs; many: a block per token
     const int hpb = tokens >= 256 ? H : 1;
-    const int threads = hpb == 1 ? 64 : 128;
+    const int threads = 128;          // the same in both layouts: the latent norm's sum is taken over the block
 #define LP_GO(T)                                                                                                             \
     ri_launch_pdl(latent_prep_kernel<T>, dim3(tokens, (H + hpb - 1) / hpb + 1), dim3(threads), 0, stream, (const T*)proj, ld, \
                   q_col, dkv_col, (const T*)qa, (T*)qf, (T*)pool, page_table, tok_seq, tok_pos, seq_slot, gain, eps, table,  \

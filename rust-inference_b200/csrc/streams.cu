@@ -195,8 +195,7 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
     RI_REQUIRE(smem <= 200 * 1024, "stream_norm: a row of %d elements does not fit in shared memory (limit 51200)", dim);
     int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
     const int write_back = rows ? 0 : 1;
-    // rows of whole float4s at aligned addresses, up to 8 streams: the vector kernel (many rows: smaller blocks,
-    // several of which share an SM)
+    // rows of whole float4s at aligned addresses, up to 8 streams: the vector kernel
     const uintptr_t al = (uintptr_t)resid | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)out;
     const int unit = dtype == RI_DTYPE_F32 ? 15 : 7;
     const bool vec = dim % 4 == 0 && streams <= 8 && (((uintptr_t)resid | (uintptr_t)gain) & 15) == 0 &&
@@ -204,8 +203,8 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
     (void)al;
     if (vec) {
         const int nvec = dim / 4;
-        threads = n_rows >= 256 ? 256 : (nvec >= 512 ? 512 : ((nvec + 31) / 32) * 32);
-        threads = nvec < threads ? ((nvec + 31) / 32) * 32 : threads;
+        // by the row length alone: the order of a row's additions must not depend on how many rows the step has
+        threads = nvec >= 256 ? 256 : ((nvec + 31) / 32) * 32;
     }
     RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "stream_norm: unknown dtype %d", dtype);
     cudaError_t e = cudaSuccess;

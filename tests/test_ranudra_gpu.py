@@ -93,7 +93,7 @@ def test_linear_heads_float32_is_exact_in_order():
 
 # ---- gated linear attention -----------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H, dim, vdim", [(2, 12, 20), (1, 33, 70), (3, 64, 130)])
+@pytest.mark.parametrize("H, dim, vdim", [(2, 12, 20), (1, 33, 70), (3, 64, 130), (2, 128, 33), (1, 136, 40)])
 def test_gla_recurrence_and_state(H, dim, vdim, dtype):
     """Two sequences of unequal length in one call; then the same tokens in two calls (the state carries over, bit
     for bit in float32); slots used again start from zero."""
