@@ -81,7 +81,8 @@ struct __align__(1024) SkinnySmem {
 template <int NT, typename OutT, bool SWIGLU, int STAGES>
 __global__ void __launch_bounds__(32 * SK_WARPS, STAGES == SK_STAGES ? SK_MIN_BLOCKS : 2)
 linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ y, int M, int N,
-                     int K, int early_from, int* __restrict__ err) {
+                     int K, int early_from, int act, int* __restrict__ err) {
+    // act (without SWIGLU): 0 nothing, 1 the square of relu, 2 gelu in its tanh form, on the float32 sums before the store
     extern __shared__ __align__(16) unsigned char sk_raw[];
     SkinnySmem<STAGES>& sm = *reinterpret_cast<SkinnySmem<STAGES>*>(sk_raw + ((1024u - (smem_u32(sk_raw) & 1023u)) & 1023u));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -205,6 +206,12 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
             float v = 0.0f;
 #pragma unroll
             for (int wi = 0; wi < SK_WARPS; wi++) v += sm.part[wi][row][tok];
+            if (act == 1) {
+                v = fmaxf(v, 0.0f);
+                v *= v;
+            } else if (act == 2) {
+                v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+            }
             st_f(y + (size_t)tok * N + n0 + row, v);
         }
     }
@@ -255,8 +262,8 @@ static int weight_tensor_map(const CUtensorMap** out, const void* w, int N, int 
 }
 
 template <int NT, typename OutT, bool SWIGLU, int STAGES>
-static int launch_skinny_ring(const CUtensorMap* map, dim3 grid, int early_from, const void* x, void* y, int M, int N, int K, int* err,
-                              cudaStream_t stream) {
+static int launch_skinny_ring(const CUtensorMap* map, dim3 grid, int early_from, const void* x, void* y, int M, int N, int K, int act,
+                              int* err, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, OutT, SWIGLU, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -265,12 +272,12 @@ static int launch_skinny_ring(const CUtensorMap* map, dim3 grid, int early_from,
         configured = true;
     }
     ri_launch_pdl(linear_skinny_kernel<NT, OutT, SWIGLU, STAGES>, grid, dim3(32 * SK_WARPS), SK_SMEM_BYTES(STAGES), stream, (const bf16*)x,
-                  *map, (OutT*)y, M, N, K, early_from, err);
+                  *map, (OutT*)y, M, N, K, early_from, act, err);
     return 0;
 }
 
 template <int NT, typename OutT, bool SWIGLU>
-static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int* err, cudaStream_t stream) {
+static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int act, int* err, cudaStream_t stream) {
     const CUtensorMap* map = nullptr;
     int rc = weight_tensor_map(&map, w, N, K);
     if (rc) return rc;
@@ -284,20 +291,22 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
     }
 #ifndef SK_NO_DEEP_RING      // (-DSK_NO_DEEP_RING: two stages everywhere, for comparisons)
     // a grid of at most two blocks per SM: the deeper ring (its blocks are all on the SMs at once: early_from 0)
-    if ((long long)grid.x <= 2ll * sms) return launch_skinny_ring<NT, OutT, SWIGLU, SK_DEEP_STAGES>(map, grid, 0, x, y, M, N, K, err, stream);
+    if ((long long)grid.x <= 2ll * sms) return launch_skinny_ring<NT, OutT, SWIGLU, SK_DEEP_STAGES>(map, grid, 0, x, y, M, N, K, act, err, stream);
 #endif
     const long long resident = (long long)sms * SK_MIN_BLOCKS;                // blocks on the device at once
     const int early_from = (long long)grid.x > resident ? (int)((long long)grid.x - resident) : 0;
-    return launch_skinny_ring<NT, OutT, SWIGLU, SK_STAGES>(map, grid, early_from, x, y, M, N, K, err, stream);
+    return launch_skinny_ring<NT, OutT, SWIGLU, SK_STAGES>(map, grid, early_from, x, y, M, N, K, act, err, stream);
 }
 
 extern "C" int ri_linear_skinny_max_tokens() { return 16; }
 
 // out_f32: 0 = bfloat16 output, 1 = float32 output.  swiglu: 1 = w holds gate and up rows in alternating
 // blocks of 8 and y [M, N/2] gets silu(gate) * up (bfloat16 only).
-extern "C" int ri_linear_skinny(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int swiglu,
-                                int* err_flag, cudaStream_t stream) {
+// act: an activation on the outputs before they are stored (0 none, 1 relu squared, 2 gelu in its tanh form); not with swiglu.
+extern "C" int ri_linear_skinny_act(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int swiglu,
+                                    int act, int* err_flag, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
+    RI_REQUIRE(act >= 0 && act <= 2 && !(act && swiglu), "linear_skinny: activation %d (with the SiLU gate: %d)", act, swiglu);
     RI_REQUIRE(M > 0 && N > 0 && K > 0, "linear_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
     RI_REQUIRE(M <= 16, "linear_skinny: at most 16 tokens, got %d", M);
     RI_REQUIRE(K % 8 == 0, "linear_skinny: K=%d must be a multiple of 8", K);
@@ -305,13 +314,18 @@ extern "C" int ri_linear_skinny(const void* x, const void* w, void* y, int M, in
     int rc;
     if (swiglu) {
         RI_REQUIRE(!out_f32 && N % 16 == 0, "linear_skinny: the fused SiLU-gate epilogue needs bfloat16 output and N a multiple of 16 (N=%d)", N);
-        rc = M <= 8 ? launch_skinny<1, bf16, true>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<2, bf16, true>(x, w, y, M, N, K, err_flag, stream);
+        rc = M <= 8 ? launch_skinny<1, bf16, true>(x, w, y, M, N, K, 0, err_flag, stream) : launch_skinny<2, bf16, true>(x, w, y, M, N, K, 0, err_flag, stream);
     } else if (M <= 8) {
-        rc = out_f32 ? launch_skinny<1, float, false>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<1, bf16, false>(x, w, y, M, N, K, err_flag, stream);
+        rc = out_f32 ? launch_skinny<1, float, false>(x, w, y, M, N, K, act, err_flag, stream) : launch_skinny<1, bf16, false>(x, w, y, M, N, K, act, err_flag, stream);
     } else {
-        rc = out_f32 ? launch_skinny<2, float, false>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<2, bf16, false>(x, w, y, M, N, K, err_flag, stream);
+        rc = out_f32 ? launch_skinny<2, float, false>(x, w, y, M, N, K, act, err_flag, stream) : launch_skinny<2, bf16, false>(x, w, y, M, N, K, act, err_flag, stream);
     }
     if (rc) return rc;
     RI_CHECK_LAUNCH("linear_skinny");
     return 0;
+}
+
+extern "C" int ri_linear_skinny(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int swiglu,
+                                int* err_flag, cudaStream_t stream) {
+    return ri_linear_skinny_act(x, w, y, M, N, K, out_f32, swiglu, 0, err_flag, stream);
 }

@@ -43,6 +43,7 @@ _SIGNATURES = {
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode_sink"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P, _P],
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    ("linear_skinny", "ri_linear_skinny_act"): [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _I, _P, _P],
@@ -55,6 +56,8 @@ _NO_TCGEN05 = os.environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == "1"   # for co
 # Qwen3-8B shapes, 0.3 % at batch 8); RUST_INFERENCE_B200_FUSED_SWIGLU=0 takes the separate kernel, for comparisons
 _FUSED_SWIGLU = os.environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU", "1") != "0"
 _WEIGHT_HINTS = os.environ.get("RUST_INFERENCE_B200_WEIGHT_HINTS", "1") != "0"
+# likewise an activation after a product of a handful of tokens (RUST_INFERENCE_B200_FUSED_ACT=0: a kernel of its own)
+_FUSED_ACT = os.environ.get("RUST_INFERENCE_B200_FUSED_ACT", "1") != "0"
 # Up to here the bfloat16 linear is this package's mma.sync weight-streaming kernel whatever the matrix; the kernel takes
 # up to 16 tokens, and from 13 to 16 it is taken for the matrices whose grid of 16-row blocks sits well on the SMs: all
 # blocks there at once, and either at most two per SM (they then have the ring of three stages) or nearly three
@@ -494,6 +497,24 @@ def _takes_stream_tc(M: int, N: int, K: int) -> bool:
     """Whether a bfloat16 linear of M tokens (more than the mma.sync kernel takes) runs on the tcgen05 streaming kernel."""
     return M <= STREAM_TC_MAX_TOKENS and K % 8 == 0 and (
         _STREAM_TC == "1" or N >= STREAM_TC_WIDE or (M <= STREAM_TC_SMALL and _STREAM_TC != "0"))
+
+
+def linear_act(x: torch.Tensor, w: torch.Tensor, act: str) -> torch.Tensor:
+    """act(x w^T) with ``act`` one of ``ACTIVATIONS``.  A handful of bfloat16 tokens run as one kernel (the
+    weight-streaming product applies the activation to its float32 sums before it stores them); otherwise the product
+    and ``activation`` run one after the other."""
+    if act not in ACTIVATIONS:
+        raise KernelError(f"activation {act!r} is not built (known: {', '.join(sorted(ACTIVATIONS))})")
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype == torch.bfloat16 and w.shape[1] == K and _FUSED_ACT and _takes_skinny(M, N, K, x.device):
+        _need(x, "x")
+        _need(w, "w", x.dtype)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        _call("linear_skinny", "ri_linear_skinny_act", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, 0, 0,
+              ACTIVATIONS[act] + 1, error_flag(x.device).data_ptr(), _stream())
+        return y
+    return activation(linear(x, w), act)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:

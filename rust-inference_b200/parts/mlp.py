@@ -70,9 +70,7 @@ class DenseFF(FeedForward):
         return self.up
 
     def __call__(self, x, ctx):
-        with section("mlp up"):
-            z = ops.linear(x, self.up)
-        with section("mlp act"):
-            z = ops.activation(z, self.spec.activation)
+        with section("mlp up/act"):
+            z = ops.linear_act(x, self.up, self.spec.activation)
         with section("mlp down"):
             return ops.linear(z, self.down)

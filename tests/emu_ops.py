@@ -14,7 +14,7 @@ import torch
 
 __all__ = ["embed", "rmsnorm", "add_rows", "silu_mul", "linear_swiglu", "linear", "qk_norm_rope_append", "attention", "argmax",
            "sample", "mark_seen", "stream_norm", "activation", "gate_heads", "linear_heads", "latent_prep", "gla_recurrent",
-           "head_norm_gate"]
+           "head_norm_gate", "linear_act"]
 
 
 def embed(ids, table, scale=1.0, copies=1):
@@ -46,6 +46,10 @@ def activation(x, kind):
     if kind == "relu2":
         return (torch.clamp(f, min=0.0) ** 2).to(x.dtype)
     return (0.5 * f * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (f + 0.044715 * f ** 3)))).to(x.dtype)
+
+
+def linear_act(x, w, act):
+    return activation(linear(x, w), act)
 
 
 def _gate(z, fn):

@@ -67,6 +67,14 @@ def test_embedding_activation_and_gates(dtype):
         xd = x.double().cpu().numpy()
         _close(ops.activation(x, "relu2"), np.maximum(xd, 0) ** 2, dtype, "relu2")
         _close(ops.activation(x, "gelu_tanh"), 0.5 * xd * (1 + np.tanh(np.sqrt(2 / np.pi) * (xd + 0.044715 * xd ** 3))), dtype, "gelu")
+    # the activation in the product's epilogue (a handful of bfloat16 tokens) and as a kernel of its own (more)
+    w = _t(rng.standard_normal((40, 64)) * 0.3, dtype)
+    for m in (3, 12, 70):
+        x = _t(rng.standard_normal((m, 64)), dtype)
+        z = x.double().cpu().numpy() @ w.double().cpu().numpy().T
+        _close(ops.linear_act(x, w, "relu2"), np.maximum(z, 0) ** 2, dtype, f"relu2 after a product of {m} tokens")
+        _close(ops.linear_act(x, w, "gelu_tanh"), 0.5 * z * (1 + np.tanh(np.sqrt(2 / np.pi) * (z + 0.044715 * z ** 3))), dtype,
+               f"gelu after a product of {m} tokens")
     wide = _t(rng.standard_normal((6, 50)) * 2, dtype)                 # gates are columns of a wider matrix
     wd = wide.double().cpu().numpy()
     for cols, per_head in ((slice(5, 9), True), (slice(10, 34), False)):
