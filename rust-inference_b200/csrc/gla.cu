@@ -18,7 +18,7 @@
 #include "common.cuh"
 
 #define GLA_TILE 64
-#define GLA_COLS 512            // threads per block of the register kernel
+#define GLA_COLS 256            // threads per block of the register kernel
 
 __device__ __forceinline__ float gla_decay(float z, float inv_tau) {
     // log(sigmoid(z)) = min(z, 0) - log1p(exp(-|z|))
@@ -26,12 +26,12 @@ __device__ __forceinline__ float gla_decay(float z, float inv_tau) {
     return expf(ls * inv_tau);
 }
 
-// The kernel for heads of up to 128 key channels.  A block of 512 threads owns 32 value columns of the state, and
+// The kernel for heads of up to 128 key channels.  A block of 256 threads owns 16 value columns of the state, and
 // sixteen threads share a column: each keeps a sixteenth of the column's key channels in registers (DIMC / 16 of
 // them, DIMC the head's key channels rounded up to 64 or 128; channels past `dim` hold zeros and stay zero).  The
 // sixteen are four neighbouring lanes in each of four warps (part p = 4 (warp % 4) + lane % 4 has channels
 // 64 c + 4 p .. + 3 for c = 0, 1, ..; warps 4 i .. 4 i + 3 own columns 8 i .. 8 i + 7), so that a warp's loads and
-// stores of the state cover 8 neighbouring columns, and what the block stages per token serves 32 columns.
+// stores of the state cover 8 neighbouring columns, and what the block stages per token serves 16 columns.
 // Many small threads instead of few large ones: the recurrence has little to do in parallel (heads x columns), and
 // this way a prompt of one sequence still puts some warps on every SM.
 // The block stages the decay, key and scaled query of GROUP tokens in shared memory (two buffers): the loads of the
@@ -260,11 +260,11 @@ extern "C" int ri_gla_recurrent(const void* proj, long long ld, int q_col, int k
                           q_col, k_col, v_col, (const T*)z, bias, 1.0f / tau, qscale, state, o, seq_slot, seq_start, H,    \
                           dim, vdim);                                                                                      \
         } while (0)
-    // tokens staged together: many, so that a trip to memory is paid once per 16 tokens
+    // tokens staged together: many, so that a trip to memory is paid once per 32 (16) tokens
 #define GLA_REG(T, DIMC)                                                                                                   \
         do {                                                                                                               \
             if (single) GLA_REG1(T, DIMC, 1);                                                                              \
-            else GLA_REG1(T, DIMC, 16);                                                                 \
+            else GLA_REG1(T, DIMC, (DIMC > 64 ? 16 : 32));                                                                 \
         } while (0)
 #define GLA_BY_DIM(T)                                                                                                      \
         do {                                                                                                               \
