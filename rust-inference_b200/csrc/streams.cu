@@ -196,11 +196,9 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
     int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
     const int write_back = rows ? 0 : 1;
     // rows of whole float4s at aligned addresses, up to 8 streams: the vector kernel
-    const uintptr_t al = (uintptr_t)resid | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)out;
     const int unit = dtype == RI_DTYPE_F32 ? 15 : 7;
     const bool vec = dim % 4 == 0 && streams <= 8 && (((uintptr_t)resid | (uintptr_t)gain) & 15) == 0 &&
                      (((uintptr_t)delta | (uintptr_t)out) & unit) == 0;
-    (void)al;
     if (vec) {
         const int nvec = dim / 4;
         // by the row length alone: the order of a row's additions must not depend on how many rows the step has
