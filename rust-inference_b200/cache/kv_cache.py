@@ -33,6 +33,7 @@ class LayerCache:
     page_size: int
     state: Optional[torch.Tensor]
     writes: bool = True
+    more_state: tuple = ()
 
 
 class _Group:
@@ -74,12 +75,12 @@ class Cache:
         by_need: Dict[tuple, List[int]] = {}
         for i, r in enumerate(self.requests):
             if r is not None and r.kv_heads > 0:
-                by_need.setdefault((r.kv_heads, r.head_dim, r.window, r.shared_kv), []).append(i)
+                by_need.setdefault((r.kv_heads, r.head_dim, r.mask, r.shared_kv), []).append(i)
         # the bookkeeping of slots, pages and lengths is one C++ object (csrc/host_cache.cpp)
         self.host = HostCache(num_slots, num_pages, self.max_pages_per_seq, page_size,
                               [need[2] for need in by_need])
         self.slots = self.host.slots
-        self._any_window = any(need[2] > 0 for need in by_need)
+        self._any_window = any(need[2] != 0 for need in by_need)
         for (need, entries), pages in zip(by_need.items(), self.host.groups):
             g = _Group(self.requests[entries[0]], entries, pages, num_slots, num_pages, self.max_pages_per_seq,
                        page_size, dtype, self.device)
@@ -90,12 +91,20 @@ class Cache:
         for i, r in enumerate(self.requests):
             if r is not None and r.state_shape:
                 self.state[i] = torch.zeros((num_slots,) + tuple(r.state_shape), dtype=r.state_dtype, device=self.device)
+        self.more_state: Dict[int, tuple] = {}
+        for i, r in enumerate(self.requests):
+            if r is not None and r.more_state:
+                self.more_state[i] = tuple(torch.zeros((num_slots,) + tuple(shape), dtype=dt, device=self.device)
+                                           for shape, dt in r.more_state)
 
     # ---- slots ---------------------------------------------------------------------------
     def alloc_slot(self) -> int:
         s = self.host.alloc_slot()
         for t in self.state.values():
             t[s].zero_()
+        for ts in self.more_state.values():
+            for t in ts:
+                t[s].zero_()
         return s
 
     def free_slot(self, slot: int) -> None:
@@ -130,12 +139,12 @@ class Cache:
 
     # ---- views -----------------------------------------------------------------------------
     def layer(self, entry: int, writes: bool = True) -> LayerCache:
-        state = self.state.get(entry)
+        state, more = self.state.get(entry), self.more_state.get(entry, ())
         if entry in self._where:
             gi, j = self._where[entry]
             g = self.groups[gi]
-            return LayerCache(g.k[j], g.v[j], g.table_dev, self.page_size, state, writes)
-        return LayerCache(None, None, None, self.page_size, state, writes)
+            return LayerCache(g.k[j], g.v[j], g.table_dev, self.page_size, state, writes, more)
+        return LayerCache(None, None, None, self.page_size, state, writes, more)
 
     def bytes_per_token(self) -> int:
         es = torch.empty((), dtype=self.dtype).element_size()

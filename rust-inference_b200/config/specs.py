@@ -27,14 +27,15 @@ class RMSNormSpec:
 
 @dataclass(frozen=True)
 class LayerNormSpec:
-    """y = (x - mean) / sqrt(var + eps) * gain over ``size`` elements, var the mean squared deviation; no bias.
+    """y = (x - mean) / sqrt(var + eps) * gain (+ bias) over ``size`` elements, var the mean squared deviation.
 
     ``weight_name`` is the local name of the gain tensor; empty where the checkpoint names that tensor by the
-    norm's prefix alone."""
+    norm's prefix alone.  ``bias_name``: the local name of the bias tensor; empty for a norm without bias."""
     size: int
     eps: float
     weight_name: str = "weight"
     kind: str = "layernorm"
+    bias_name: str = ""
 
 
 @dataclass(frozen=True)
@@ -82,7 +83,11 @@ class AttentionSpec:
 
     ``qk_norm`` is the per-head norm applied to queries and keys before the
     position encoding (None for none); ``window`` > 0 limits a query to the last
-    ``window`` keys; ``scale`` 0 means 1/sqrt(head_dim).
+    ``window`` keys; ``scale`` 0 means 1/sqrt(head_dim).  ``chunk`` > 0 (instead of a window): a query sees the
+    keys of its own chunk of that many positions, chunks counted from the sequence's start.  ``sink``: a learned
+    term per head in the softmax's denominator, with no key and no value.  ``v_head_dim`` > 0: values (and the
+    heads' outputs) have that size instead of ``head_dim``.  ``names``: the tensors' local names as
+    (q, k, v, o, sink) where they are not the default ones.
     """
     hidden_size: int
     num_heads: int
@@ -93,6 +98,10 @@ class AttentionSpec:
     window: int = 0
     scale: float = 0.0
     kind: str = "attention"
+    chunk: int = 0
+    sink: bool = False
+    v_head_dim: int = 0
+    names: Tuple[str, ...] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "sink")
 
 
 @dataclass(frozen=True)
@@ -136,6 +145,64 @@ class GLASpec:
 
 
 @dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule: per head a state [dim, vdim] that each token decays per key channel, corrects towards
+    its value along its key (with strength beta) and reads with its query.  ``num_heads`` value heads share
+    ``num_qk_heads`` query/key heads; q, k and v pass a causal convolution of ``conv`` taps per channel and silu, q and
+    k are made unit vectors; the decay comes from a low-rank projection (inner size ``decay_rank``), a bias and a rate
+    per head; the heads' outputs are RMS-normed over ``vdim`` (one gain for all heads, ``eps``) and gated with the
+    sigmoid of another low-rank projection (``gate_rank``)."""
+    hidden_size: int
+    num_heads: int
+    num_qk_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    decay_rank: int
+    gate_rank: int
+    eps: float
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side on the same input: ``left_scale`` * left + ``right_scale`` * right.  Their tensors
+    carry the prefixes "left." and "right."."""
+    left: object
+    right: object
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
+class GatedFFSpec:
+    """down(f(gate x) * up x), no biases; ``gate``: "silu", "gelu_tanh", or "clamped_swish"
+    (g sigmoid(alpha g) (u + 1) with g = min(gate x, limit) and u = clamp(up x, -limit, limit))."""
+    hidden_size: int
+    intermediate_size: int
+    gate: str = "gelu_tanh"
+    limit: float = 0.0
+    alpha: float = 1.702
+    kind: str = "gated"
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """A routed feed-forward: ``experts`` gated feed-forwards (record ``expert``, tensors "e<i>.") of which a token
+    uses ``top``; the router also has ``identity`` outputs after the experts' whose "expert" returns its input.
+    Scores are the softmax over all router outputs; the choice adds a learned correction to them, the weights are the
+    chosen scores divided by their sum.  ``shared`` (or None): a feed-forward that every token takes, added."""
+    hidden_size: int
+    experts: int
+    top: int
+    expert: object
+    identity: int = 0
+    shared: object = None
+    kind: str = "moe"
+
+
+@dataclass(frozen=True)
 class DenseFFSpec:
     """down(act(up x)), no biases; ``activation``: "relu2" (the square of relu) or "gelu_tanh"."""
     hidden_size: int
@@ -152,6 +219,7 @@ class HyperConnectionSpec:
     streams: int
     learned: bool = True
     kind: str = "hyper"
+    scale: float = 1.0          # without weights: x <- x + scale * y
 
 
 @dataclass(frozen=True)
@@ -174,11 +242,26 @@ class EmbeddingSpec:
 
 
 @dataclass(frozen=True)
+class PairHashEmbeddingSpec:
+    """h[t] = table[ids[t]] + pairs[(ids[t-1] * mul_prev + ids[t] * mul_cur) mod buckets]; a sequence's first token
+    takes row ``buckets`` of ``pairs`` [buckets + 1, hidden].  The previous token is per-sequence state.
+    ``pairs_name``: the pair table's tensor name."""
+    vocab_size: int
+    hidden_size: int
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    pairs_name: str = "bigram"
+    kind: str = "pair_hash"
+
+
+@dataclass(frozen=True)
 class HeadSpec:
-    """logits = x W^T in float32, no bias, no soft-cap; W may be the embedding table (tied)."""
+    """logits = x W^T * scale in float32, no bias, no soft-cap; W may be the embedding table (tied)."""
     vocab_size: int
     hidden_size: int
     kind: str = "linear"
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -223,6 +306,22 @@ class StreamLayerSpec:
 
 
 @dataclass(frozen=True)
+class ParallelLayerSpec:
+    """One block whose mixer and feed-forward (``ffn`` None: none) both read the one norm's output, and whose outputs
+    join the residual together through ``link`` (``arrangement`` "parallel").  ``names`` maps the parts ("norm",
+    "mixer", "ffn", "link") to the prefixes of their tensors."""
+    mixer: object
+    norm: object
+    link: object
+    ffn: object = None
+    names: Tuple[Tuple[str, str], ...] = ()
+    arrangement: str = "parallel"
+
+    def prefix(self, part: str) -> str:
+        return dict(self.names).get(part, "")
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One execution of a layer.  ``layer`` indexes ``ModelSpec.layers``;
     ``cache`` names the cache entry (an index into the list of cache entries)
@@ -255,6 +354,9 @@ class ModelSpec:
     # name with "weight" replaced by theirs
     embedding: object = None
     head: object = None
+    # tensors of the embedding or the head whose names do not derive from ``embedding_name`` / ``head_name``:
+    # (local name, full name) pairs
+    end_names: Tuple[Tuple[str, str], ...] = ()
 
     def embedding_record(self):
         return self.embedding or EmbeddingSpec(self.vocab_size, self.hidden_size)

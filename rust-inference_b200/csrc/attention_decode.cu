@@ -115,7 +115,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     float* comb = reinterpret_cast<float*>(smem_raw + sizeof(DecodeSmem));
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int len = seq_len[b];                      // keys 0 .. len-1; the query is at position len-1
-    const int first_key = (window > 0 && len - window > 0) ? len - window : 0;
+    const int first_key = ri_first_visible(len - 1, window);
     const int c0 = chunk * AD_CHUNK;
     if (c0 >= len || c0 + AD_CHUNK <= first_key) return;       // nothing of this chunk is visible
     const int G = H / KV;
@@ -391,7 +391,7 @@ __device__ __forceinline__ int warp_sum_int(int v) { return __reduce_add_sync(0x
 
 // the pages that the query of a sequence of `len` keys sees: [p_first, p_first + n)
 __device__ __forceinline__ int stream_visible(int len, int window, int max_pages, int& first_key, int& p_first) {
-    first_key = (window > 0 && len - window > 0) ? len - window : 0;
+    first_key = ri_first_visible(len - 1, window);
     p_first = first_key / AD_PAGE;
     int p_last = (len + AD_PAGE - 1) / AD_PAGE;
     p_last = p_last < max_pages ? p_last : max_pages;     // no partial result has a place beyond (the merge reports it)
@@ -868,7 +868,7 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
     __shared__ int s_cnt[2][MW];
     pdl_trigger();
     const int len = seq_len[b];                          // a table of the step, not the work of the kernel before
-    const int first_key = (window > 0 && len - window > 0) ? len - window : 0;
+    const int first_key = ri_first_visible(len - 1, window);
     int c_lo = first_key / AD_CHUNK, c_hi = (len + AD_CHUNK - 1) / AD_CHUNK;           // [c_lo, c_hi)
     const bool too_long = c_hi > max_chunks;
     int stride = max_chunks;                             // partial results a head has room for
@@ -1079,7 +1079,6 @@ extern "C" int ri_attention_decode_sink(const void* q, const void* k_pool, const
     RI_REQUIRE(page_size == AD_PAGE, "attention_decode: pages of %d tokens, this kernel needs %d", page_size, AD_PAGE);
     RI_REQUIRE(H > 0 && KV > 0 && H % KV == 0, "attention_decode: %d heads over %d kv heads", H, KV);
     RI_REQUIRE(max_chunks > 0 && seqs <= 65535 && KV <= 65535, "attention_decode: bad grid");
-    RI_REQUIRE(window >= 0, "attention_decode: negative window");
     RI_REQUIRE((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0, "attention_decode: q and the pools must be 16-byte aligned");
 #if ADS_OK && !defined(AD_NO_STREAM)
     if (H / KV <= AD_ROWS && scale > 0.0f && seqs <= ADS_MAX_SEQS) {

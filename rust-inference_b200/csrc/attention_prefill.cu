@@ -83,7 +83,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     const int r_base = tile * PF_BM;
     const int rows = min(PF_BM, n_new - r_base);
     const int pos_first = len - n_new + r_base, pos_last = pos_first + rows - 1;
-    const int key_lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int key_lo = ri_first_visible(pos_first, window);
     const int kb_lo = key_lo / PF_BN, kb_hi = pos_last / PF_BN;
     const int kvh = h / (H / KV);
     const int* table = page_table + (size_t)seq_slot[b] * mpps;
@@ -136,7 +136,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
         }
         // ---- scale, mask where the block touches an edge, online softmax -----------------------------
         const int k0 = kb * PF_BN;
-        const bool edge = (k0 + PF_BN - 1 > pos_first) || (window > 0 && k0 < pos_last - window + 1);
+        const bool edge = (k0 + PF_BN - 1 > pos_first) || (window != 0 && k0 < ri_first_visible(pos_last, window));
         float mx[2] = {m[0], m[1]};
 #pragma unroll
         for (int t = 0; t < PF_BN / 8; t++)
@@ -146,7 +146,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                 if (edge) {
                     int key = k0 + t * 8 + qc * 2 + (e & 1);
                     int p = my_pos[e >> 1];
-                    bool vis = key <= p && (window <= 0 || key > p - window);
+                    bool vis = key <= p && key >= ri_first_visible(p, window);
                     val = vis ? val : -FLT_MAX;
                 }
                 s[t][e] = val;
@@ -229,7 +229,6 @@ extern "C" int ri_attention_prefill(const void* q, const void* k_pool, const voi
     RI_REQUIRE(page_size == PF_PAGE, "attention_prefill: pages of %d tokens, this kernel needs %d", page_size, PF_PAGE);
     RI_REQUIRE(H > 0 && KV > 0 && H % KV == 0, "attention_prefill: %d heads over %d kv heads", H, KV);
     RI_REQUIRE(seqs <= 65535 && H <= 65535, "attention_prefill: bad grid");
-    RI_REQUIRE(window >= 0, "attention_prefill: negative window");
     // v_dims: how many leading value elements are wanted (0: all); values that are the keys (v_pool == k_pool) are
     // read from the key tiles
     const int shared_kv = v_pool == k_pool ? 1 : 0;

@@ -167,7 +167,7 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, con
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int len = seq_len[b];
     const int pos0 = len - n_new + r_base, pos_last = pos0 + nq - 1;       // positions of the tile's queries
-    const int key_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int key_lo = ri_first_visible(pos0, window);
     const int* table = page_table + (size_t)seq_slot[b] * mpps;
 
     // row = i * ng + g: new token r_base + i, query head kvh * G + g0 + g
@@ -217,7 +217,7 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, con
         for (int unit = warp; unit < nq * pairs; unit += AR_WARPS) {
             const int i = unit / pairs, g_first = 2 * (unit - i * pairs);
             const int pos = pos0 + i;
-            const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+            const int first = ri_first_visible(pos, window);
             const int j_lo = max(first - key0, 0), j_hi = min(pos - key0, width - 1);       // the token's keys in this strip
             if (j_lo > j_hi) continue;                                // none: the rows' state stays as it is
             const int row_a = i * ng + g_first;
@@ -291,7 +291,6 @@ extern "C" int ri_attention_rows(const void* q, const void* k_pool, const void* 
     RI_REQUIRE(seqs > 0 && max_new > 0 && H > 0 && KV > 0 && Dh > 0 && page_size > 0 && mpps > 0, "attention_rows: bad sizes");
     RI_REQUIRE(H % KV == 0, "attention_rows: %d heads are not a multiple of %d kv heads", H, KV);
     RI_REQUIRE(Dh <= AR_MAX_DH, "attention_rows: head_dim %d exceeds the limit %d", Dh, AR_MAX_DH);
-    RI_REQUIRE(window >= 0, "attention_rows: negative window");
     const bool f32 = dtype == RI_DTYPE_F32;
     RI_REQUIRE(f32 || dtype == RI_DTYPE_BF16, "attention_rows: unknown dtype %d", dtype);
     // vector loads need rows of the pools and of q that start on 16 bytes (float32) or 8 bytes (bfloat16)

@@ -36,6 +36,9 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "streams": ("streams.cu", "common.cuh"),
     "latent_attention": ("latent_attention.cu", "common.cuh"),
     "gla": ("gla.cu", "common.cuh"),
+    "pair_embedding": ("pair_embedding.cu", "common.cuh"),
+    "delta_rule": ("delta_rule.cu", "common.cuh"),
+    "moe": ("moe.cu", "common.cuh", "mma_helpers.cuh"),
     "sampling": ("sampling.cu", "common.cuh"),
     "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh"),

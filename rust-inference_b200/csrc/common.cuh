@@ -106,6 +106,17 @@ __device__ __forceinline__ bool ri_mbar_wait(unsigned long long* bar, unsigned p
     }
 }
 
+// ---- which keys a query sees ---------------------------------------------------------------------
+// The attention kernels take one integer for the mask beside causality.  `window` > 0: the query at position
+// `pos` sees the last `window` keys (pos - window + 1 .. pos).  `window` < 0: a mask of chunks of -window positions
+// counted from position 0 of the sequence: the query sees the keys of its own chunk up to itself
+// (pos - pos % size .. pos).  0: every key up to pos.  Both bounds never decrease with pos.
+__host__ __device__ __forceinline__ int ri_first_visible(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos < 0 ? 0 : pos - pos % (-window);
+    return 0;
+}
+
 __device__ __forceinline__ float ld_f(const float* p) { return *p; }
 __device__ __forceinline__ float ld_f(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void st_f(float* p, float v) { *p = v; }

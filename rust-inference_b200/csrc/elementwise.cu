@@ -548,3 +548,65 @@ extern "C" int ri_gate_heads(void* x, const void* g, long long ldg, int tokens, 
     RI_CHECK_LAUNCH("gate_heads");
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// A gated feed-forward's middle: out[m, c] = f(g) * u', with g and u the gate and up values of channel c of row m of
+// `gu` [rows, 2 inter] (gate and up columns alternate in blocks of `block` channels).
+//   kind 0: silu(g) u;   kind 1: gelu_tanh(g) u, gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)));
+//   kind 2: g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+// float32 arithmetic with the full-precision functions, one rounding at the end.
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int block, size_t total, int kind,
+                                 float limit, float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    size_t m = i / inter;
+    int c = (int)(i - m * inter);
+    int gc = (c / block) * 2 * block + c % block;
+    float g = ld_f(gu + m * 2 * inter + gc);
+    float u = ld_f(gu + m * 2 * inter + gc + block);
+    float r;
+    if (kind == 0) {
+        r = (g / (1.0f + expf(-g))) * u;
+    } else if (kind == 1) {
+        r = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    } else {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        r = (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+    }
+    st_f(out + i, r);
+}
+
+extern "C" int ri_gated_act(const void* gu, void* out, int rows, int inter, int block, int kind, float limit, float alpha,
+                            int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    RI_REQUIRE(rows > 0 && inter > 0, "gated_act: bad sizes rows=%d inter=%d", rows, inter);
+    RI_REQUIRE(block > 0 && inter % block == 0, "gated_act: %d channels are not whole blocks of %d", inter, block);
+    RI_REQUIRE(kind >= 0 && kind <= 2, "gated_act: unknown kind %d", kind);
+    size_t total = (size_t)rows * inter;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == RI_DTYPE_F32) ri_launch_pdl(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, block, total, kind, limit, alpha);
+    else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, block, total, kind, limit, alpha);
+    else RI_FAIL(-1, "gated_act: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("gated_act");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// x *= factor, in place, float32 (logits that the model multiplies by a constant).
+__global__ void scale_f32_kernel(float* __restrict__ x, size_t total, float factor) {
+    pdl_trigger();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] *= factor;
+}
+
+extern "C" int ri_scale_f32(float* x, long long total, float factor, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    ri_launch_pdl(scale_f32_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, (size_t)total, factor);
+    RI_CHECK_LAUNCH("scale_f32");
+    return 0;
+}

@@ -120,8 +120,11 @@ struct Pages {
     }
     // gives back the pages that no later query of slot s can see (groups with a window)
     int release_behind_window(int s) {
-        if (window <= 0) return 0;
-        const long long first_needed = (long long)lens[s] - window + 1;      // oldest key the next query reads
+        if (window == 0) return 0;
+        // oldest key the next query (at position lens[s]) reads: the last `window` keys, or, with a negative value,
+        // the start of its chunk of -window positions counted from the sequence's start
+        const long long first_needed = window > 0 ? (long long)lens[s] - window + 1
+                                                  : (long long)lens[s] - (long long)lens[s] % (-window);
         int32_t* r = row(s);
         int n = 0, p = first_mapped[s];
         while ((long long)(p + 1) * page_size <= first_needed) {
@@ -308,7 +311,7 @@ int ri_cache_extend(void* h, int n, const int* slot, const int* news, int* befor
 // after a step: releases what no later step can read (pages behind a window)
 void ri_cache_after_step(void* h, int n, const int* slot) {
     for (Pages& g : as<HostCache>(h)->groups)
-        if (g.window > 0)
+        if (g.window != 0)
             for (int i = 0; i < n; i++) g.release_behind_window(slot[i]);
 }
 int ri_cache_free_pages(void* h, int if_no_group) {

@@ -1,0 +1,378 @@
+// A routed feed-forward (mixture of experts): router, plan of the step, grouped products, combination.
+//
+// `moe_route`   per token: logits z = R x (float32), scores s = softmax(z) over all N outputs of the router, choice
+//               scores s + correction, the `top` largest of them (ties: the lower index), and as weights the chosen
+//               outputs' scores s divided by their sum (+ 1e-20).  A warp per token; every sum has a fixed order.
+// `moe_plan`    the step's (token, choice) pairs grouped by expert: `perm` lists the pairs of expert 0, then of expert
+//               1 and so on (pairs whose choice is not one of the first E outputs, identity experts, are left out), and
+//               `tiles` cuts every expert's run into tiles of MOE_BM rows: (expert, first row in perm, rows).  One
+//               block; which pair lands where inside an expert's run is not fixed, and no result depends on it: a
+//               row of a product is computed alone.
+// `moe_grouped_linear`  y[out(r), :] = W[e] a[in(r), :] for every row r of every tile, W [E, N, K]; in(r) = perm[r] /
+//               div (gather: a token's row for each of its pairs) or r, out(r) = perm[r] (scatter: back to the pair's
+//               own place) or r.  float32: FMA tiles, k ascending in one accumulator per output; bfloat16: mma.sync
+//               m16n8k16 with float32 accumulators.  The grid covers the most tiles a step can have; blocks past the
+//               plan's count leave at once (the count stays on the device: no trip to the host, and the step can be
+//               replayed from a graph).
+// `moe_combine` y[t] = sum_j w[t, j] (choice j an identity expert ? x[t] : pair_out[t top + j]) (+ extra[t]),
+//               j ascending, float32, rounded once.
+#include "common.cuh"
+#include "mma_helpers.cuh"
+
+#define MOE_BM 32
+#define MOE_BN 64
+#define MOE_ROUTE_WARPS 4
+
+template <typename T>
+__global__ void __launch_bounds__(32 * MOE_ROUTE_WARPS)
+moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
+                 int* __restrict__ idx, float* __restrict__ weight, int tokens, int D, int N, int top) {
+    extern __shared__ float moe_sm[];                 // per warp: scores [N], choice scores [N]
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * MOE_ROUTE_WARPS + warp;
+    if (t >= tokens) return;
+    float* s = moe_sm + (size_t)warp * 2 * N;
+    float* c = s + N;
+    const T* xr = x + (size_t)t * D;
+    for (int n = 0; n < N; n++) {
+        const float* w = router + (size_t)n * D;
+        float acc = 0.0f;
+        for (int k = lane; k < D; k += 32) acc = fmaf(ld_f(xr + k), w[k], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) s[n] = acc;
+    }
+    __syncwarp();
+    float mx = -INFINITY;
+    for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (int n = lane; n < N; n += 32) {
+        const float e = expf(s[n] - mx);
+        s[n] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    for (int n = lane; n < N; n += 32) {
+        s[n] = s[n] / sum;
+        c[n] = s[n] + correction[n];
+    }
+    __syncwarp();
+    float picked_sum = 0.0f;
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int n = lane; n < N; n += 32)
+            if (c[n] > best) {                        // ascending n: the first of equals stays
+                best = c[n];
+                at = n;
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) {
+                best = ob;
+                at = oa;
+            }
+        }
+        if (at >= N) at = 0;                           // no finite score left (NaN inputs): still a valid index
+        if (lane == 0) {
+            idx[(size_t)t * top + j] = at;
+            weight[(size_t)t * top + j] = s[at];
+            c[at] = -INFINITY;
+        }
+        picked_sum += s[at];
+        __syncwarp();
+    }
+    if (lane == 0)
+        for (int j = 0; j < top; j++) weight[(size_t)t * top + j] /= picked_sum + 1e-20f;
+}
+
+extern "C" int ri_moe_route(const void* x, const float* router, const float* correction, int* idx, float* weight,
+                            int tokens, int D, int N, int top, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    RI_REQUIRE(tokens > 0 && D > 0 && N > 0 && top > 0 && top <= N, "moe_route: bad sizes (top %d of %d)", top, N);
+    RI_REQUIRE(N <= 4096, "moe_route: %d router outputs (up to 4096 are built)", N);
+    const size_t smem = (size_t)MOE_ROUTE_WARPS * 2 * N * sizeof(float);
+    const dim3 grid((tokens + MOE_ROUTE_WARPS - 1) / MOE_ROUTE_WARPS);
+    cudaError_t e = cudaSuccess;
+    if (dtype == RI_DTYPE_F32) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RI_FAIL((int)e, "moe_route: %s", cudaGetErrorString(e));
+        ri_launch_pdl(moe_route_kernel<float>, grid, dim3(32 * MOE_ROUTE_WARPS), smem, stream, (const float*)x, router,
+                      correction, idx, weight, tokens, D, N, top);
+    } else if (dtype == RI_DTYPE_BF16) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RI_FAIL((int)e, "moe_route: %s", cudaGetErrorString(e));
+        ri_launch_pdl(moe_route_kernel<bf16>, grid, dim3(32 * MOE_ROUTE_WARPS), smem, stream, (const bf16*)x, router,
+                      correction, idx, weight, tokens, D, N, top);
+    } else RI_FAIL(-1, "moe_route: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("moe_route");
+    return 0;
+}
+
+// ---- the plan ---------------------------------------------------------------------------------------------------------
+// meta[0] = number of tiles, meta[1] = number of rows in perm.  tiles [max_tiles][3].
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ idx, int* __restrict__ perm, int* __restrict__ tiles, int* __restrict__ meta,
+                int pairs, int E, int max_tiles) {
+    extern __shared__ int plan_sm[];                  // counts [E], offsets [E + 1], cursors [E]
+    int* counts = plan_sm;
+    int* offsets = counts + E;
+    int* cursor = offsets + E + 1;
+    pdl_trigger();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = cursor[e] = 0;
+    pdl_wait();
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = idx[p];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, n = 0;
+        for (int e = 0; e < E; e++) {
+            offsets[e] = off;
+            for (int r = 0; r < counts[e] && n < max_tiles; r += MOE_BM) {
+                tiles[3 * n] = e;
+                tiles[3 * n + 1] = off + r;
+                tiles[3 * n + 2] = min(MOE_BM, counts[e] - r);
+                n++;
+            }
+            off += counts[e];
+        }
+        offsets[E] = off;
+        meta[0] = n;
+        meta[1] = off;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = idx[p];
+        if (e >= 0 && e < E) perm[offsets[e] + atomicAdd(&cursor[e], 1)] = p;
+    }
+}
+
+extern "C" int ri_moe_max_tiles(int pairs, int E) { return (pairs + MOE_BM - 1) / MOE_BM + E; }
+
+extern "C" int ri_moe_plan(const int* idx, int* perm, int* tiles, int* meta, int pairs, int E, int max_tiles,
+                           cudaStream_t stream) {
+    if (pairs == 0) return 0;
+    RI_REQUIRE(pairs > 0 && E > 0 && max_tiles >= ri_moe_max_tiles(pairs, E), "moe_plan: bad sizes");
+    const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
+    RI_REQUIRE(smem <= 48 * 1024, "moe_plan: %d experts (up to 4095 are built)", E);
+    ri_launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, idx, perm, tiles, meta, pairs, E, max_tiles);
+    RI_CHECK_LAUNCH("moe_plan");
+    return 0;
+}
+
+// ---- grouped products ---------------------------------------------------------------------------------------------------
+template <typename TO>
+__device__ __forceinline__ void moe_store(TO* p, float v) { st_f(p, v); }
+
+// float32: 128 threads, each 4 rows x 4 columns of the 32 x 64 tile; k ascending, one accumulator per output
+template <typename TO>
+__global__ void __launch_bounds__(128)
+moe_grouped_f32_kernel(const float* __restrict__ a, long long lda, const float* __restrict__ w, TO* __restrict__ y,
+                       long long ldy, const int* __restrict__ perm, const int* __restrict__ tiles,
+                       const int* __restrict__ meta, int N, int K, int gather_div, int scatter) {
+    constexpr int BK = 16;
+    __shared__ float As[BK][MOE_BM + 1], Ws[BK][MOE_BN + 1];
+    __shared__ int s_in[MOE_BM], s_out[MOE_BM];
+    pdl_trigger();
+    pdl_wait();
+    if ((int)blockIdx.x >= meta[0]) return;
+    const int e = tiles[3 * blockIdx.x], r0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+    const int n0 = blockIdx.y * MOE_BN;
+    for (int i = threadIdx.x; i < MOE_BM; i += blockDim.x) {
+        const int p = i < rows ? perm[r0 + i] : 0;
+        s_in[i] = gather_div > 0 ? p / gather_div : r0 + i;
+        s_out[i] = scatter ? p : r0 + i;
+    }
+    __syncthreads();
+    const float* we = w + (size_t)e * N * K;
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int i = threadIdx.x; i < MOE_BM * BK; i += blockDim.x) {
+            const int r = i / BK, k = i % BK;
+            As[k][r] = (r < rows && k0 + k < K) ? a[(size_t)s_in[r] * lda + k0 + k] : 0.0f;
+        }
+        for (int i = threadIdx.x; i < MOE_BN * BK; i += blockDim.x) {
+            const int n = i / BK, k = i % BK;
+            Ws[k][n] = (n0 + n < N && k0 + k < K) ? we[(size_t)(n0 + n) * K + k0 + k] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            float av[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) av[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) wv[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = ty * 4 + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) moe_store(y + (size_t)s_out[r] * ldy + n, acc[i][j]);
+        }
+    }
+}
+
+// bfloat16: 4 warps; warp w owns columns 16 w .. 16 w + 15 of the tile and all 32 rows (2 x 2 mma tiles per k16)
+template <typename TO>
+__global__ void __launch_bounds__(128)
+moe_grouped_bf16_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ w, TO* __restrict__ y,
+                        long long ldy, const int* __restrict__ perm, const int* __restrict__ tiles,
+                        const int* __restrict__ meta, int N, int K, int gather_div, int scatter, int vec) {
+    constexpr int BK = 32, PITCH = BK + 8;
+    __shared__ __align__(16) bf16 As[MOE_BM][PITCH], Ws[MOE_BN][PITCH];
+    __shared__ int s_in[MOE_BM], s_out[MOE_BM];
+    pdl_trigger();
+    pdl_wait();
+    if ((int)blockIdx.x >= meta[0]) return;
+    const int e = tiles[3 * blockIdx.x], r0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+    const int n0 = blockIdx.y * MOE_BN;
+    for (int i = threadIdx.x; i < MOE_BM; i += blockDim.x) {
+        const int p = i < rows ? perm[r0 + i] : 0;
+        s_in[i] = gather_div > 0 ? p / gather_div : r0 + i;
+        s_out[i] = scatter ? p : r0 + i;
+    }
+    __syncthreads();
+    const bf16* we = w + (size_t)e * N * K;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int quad = lane >> 2, qc = lane & 3;
+    float acc[2][2][4] = {};
+    const bf16 zero = __float2bfloat16_rn(0.0f);
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        if (vec) {
+            {   // 32 rows x 4 pieces of 8 elements
+                const int r = threadIdx.x / 4, kc = (threadIdx.x % 4) * 8;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (r < rows && k0 + kc < K) v = *reinterpret_cast<const uint4*>(a + (size_t)s_in[r] * lda + k0 + kc);
+                *reinterpret_cast<uint4*>(&As[r][kc]) = v;
+            }
+#pragma unroll
+            for (int pass = 0; pass < 2; pass++) {
+                const int i = threadIdx.x + pass * 128;
+                const int n = i / 4, kc = (i % 4) * 8;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (n0 + n < N && k0 + kc < K) v = *reinterpret_cast<const uint4*>(we + (size_t)(n0 + n) * K + k0 + kc);
+                *reinterpret_cast<uint4*>(&Ws[n][kc]) = v;
+            }
+        } else {
+            for (int i = threadIdx.x; i < MOE_BM * BK; i += blockDim.x) {
+                const int r = i / BK, k = i % BK;
+                As[r][k] = (r < rows && k0 + k < K) ? a[(size_t)s_in[r] * lda + k0 + k] : zero;
+            }
+            for (int i = threadIdx.x; i < MOE_BN * BK; i += blockDim.x) {
+                const int n = i / BK, k = i % BK;
+                Ws[n][k] = (n0 + n < N && k0 + k < K) ? we[(size_t)(n0 + n) * K + k0 + k] : zero;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk += 16) {
+            unsigned af[2][4], bfr[2][2];
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++) {
+                af[mi][0] = *reinterpret_cast<const unsigned*>(&As[mi * 16 + quad][kk + qc * 2]);
+                af[mi][1] = *reinterpret_cast<const unsigned*>(&As[mi * 16 + quad + 8][kk + qc * 2]);
+                af[mi][2] = *reinterpret_cast<const unsigned*>(&As[mi * 16 + quad][kk + qc * 2 + 8]);
+                af[mi][3] = *reinterpret_cast<const unsigned*>(&As[mi * 16 + quad + 8][kk + qc * 2 + 8]);
+            }
+#pragma unroll
+            for (int ni = 0; ni < 2; ni++) {
+                bfr[ni][0] = *reinterpret_cast<const unsigned*>(&Ws[warp * 16 + ni * 8 + quad][kk + qc * 2]);
+                bfr[ni][1] = *reinterpret_cast<const unsigned*>(&Ws[warp * 16 + ni * 8 + quad][kk + qc * 2 + 8]);
+            }
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+                for (int ni = 0; ni < 2; ni++)
+                    mma_bf16(acc[mi][ni], af[mi][0], af[mi][1], af[mi][2], af[mi][3], bfr[ni][0], bfr[ni][1]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+        for (int ni = 0; ni < 2; ni++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int r = mi * 16 + quad + (c >> 1) * 8;
+                const int n = n0 + warp * 16 + ni * 8 + qc * 2 + (c & 1);
+                if (r < rows && n < N) moe_store(y + (size_t)s_out[r] * ldy + n, acc[mi][ni][c]);
+            }
+}
+
+// a [rows, lda] and w [E, N, K] in the compute type; y [.., ldy] float32 (out_f32) or the compute type
+extern "C" int ri_moe_grouped_linear(const void* a, long long lda, const void* w, void* y, long long ldy, const int* perm,
+                                     const int* tiles, const int* meta, int max_tiles, int N, int K, int gather_div,
+                                     int scatter, int out_f32, int dtype, cudaStream_t stream) {
+    if (max_tiles == 0) return 0;
+    RI_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && gather_div >= 0, "moe_grouped_linear: bad sizes");
+    const dim3 grid(max_tiles, (N + MOE_BN - 1) / MOE_BN);
+    RI_REQUIRE(grid.y <= 65535, "moe_grouped_linear: %d outputs are too many for one launch", N);
+    if (dtype == RI_DTYPE_F32) {
+        RI_REQUIRE(out_f32, "moe_grouped_linear: a float32 product writes float32");
+        ri_launch_pdl(moe_grouped_f32_kernel<float>, grid, dim3(128), 0, stream, (const float*)a, lda, (const float*)w,
+                      (float*)y, ldy, perm, tiles, meta, N, K, gather_div, scatter);
+    } else if (dtype == RI_DTYPE_BF16) {
+        const int vec = (K % 8 == 0 && lda % 8 == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0) ? 1 : 0;
+        if (out_f32)
+            ri_launch_pdl(moe_grouped_bf16_kernel<float>, grid, dim3(128), 0, stream, (const bf16*)a, lda, (const bf16*)w,
+                          (float*)y, ldy, perm, tiles, meta, N, K, gather_div, scatter, vec);
+        else
+            ri_launch_pdl(moe_grouped_bf16_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)a, lda, (const bf16*)w,
+                          (bf16*)y, ldy, perm, tiles, meta, N, K, gather_div, scatter, vec);
+    } else RI_FAIL(-1, "moe_grouped_linear: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("moe_grouped_linear");
+    return 0;
+}
+
+// ---- combination ----------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ pair_out, const int* __restrict__ idx, const float* __restrict__ weight,
+                   const T* __restrict__ x, const T* __restrict__ extra, T* __restrict__ y, int D, int top, int E) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < top; j++) {
+            const int e = idx[(size_t)t * top + j];
+            const float v = (e >= E) ? ld_f(x + (size_t)t * D + d) : pair_out[((size_t)t * top + j) * D + d];
+            acc = fmaf(weight[(size_t)t * top + j], v, acc);
+        }
+        if (extra) acc += ld_f(extra + (size_t)t * D + d);
+        st_f(y + (size_t)t * D + d, acc);
+    }
+}
+
+extern "C" int ri_moe_combine(const float* pair_out, const int* idx, const float* weight, const void* x, const void* extra,
+                              void* y, int tokens, int D, int top, int E, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    RI_REQUIRE(tokens > 0 && D > 0 && top > 0, "moe_combine: bad sizes");
+    if (dtype == RI_DTYPE_F32)
+        ri_launch_pdl(moe_combine_kernel<float>, dim3(tokens), dim3(256), 0, stream, pair_out, idx, weight, (const float*)x,
+                      (const float*)extra, (float*)y, D, top, E);
+    else if (dtype == RI_DTYPE_BF16)
+        ri_launch_pdl(moe_combine_kernel<bf16>, dim3(tokens), dim3(256), 0, stream, pair_out, idx, weight, (const bf16*)x,
+                      (const bf16*)extra, (bf16*)y, D, top, E);
+    else RI_FAIL(-1, "moe_combine: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("moe_combine");
+    return 0;
+}

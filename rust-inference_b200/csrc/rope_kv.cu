@@ -23,7 +23,7 @@ __global__ void qk_norm_rope_append_kernel(const T* __restrict__ qkv, T* __restr
                                            const int* __restrict__ seq_slot, const float* __restrict__ q_gain,
                                            const float* __restrict__ k_gain, float eps,
                                            const float2* __restrict__ rope, int rope_rows, int rot, int H, int KV,
-                                           int Dh, int mpps, int page_size, int num_pages, int write_kv,
+                                           int Dh, int mpps, int page_size, int num_pages, int write_kv, int pairs,
                                            int* __restrict__ err) {
     __shared__ float buf[RK_WARPS][RK_MAX_DH];
     pdl_trigger();
@@ -80,10 +80,12 @@ __global__ void qk_norm_rope_append_kernel(const T* __restrict__ qkv, T* __restr
         if (rope) {
             const float2* cs = rope + (size_t)pos * half;
             for (int d = lane; d < half; d += 32) {
-                float a = x[d], b = x[d + half];
+                // partners: half a rotated part apart, or (pairs) neighbours 2d and 2d + 1
+                const int ia = pairs ? 2 * d : d, ib = pairs ? 2 * d + 1 : d + half;
+                float a = x[ia], b = x[ib];
                 float2 c = cs[d];
-                st_f(dst + d, a * c.x - b * c.y);
-                st_f(dst + d + half, b * c.x + a * c.y);
+                st_f(dst + ia, a * c.x - b * c.y);
+                st_f(dst + ib, b * c.x + a * c.y);
             }
             for (int d = rot + lane; d < Dh; d += 32) st_f(dst + d, x[d]);
         } else {
@@ -336,11 +338,12 @@ static void launch_rope_vec(dim3 grid, cudaStream_t stream, const void* qkv, voi
                   (const float2*)rope_table, rope_rows, H, KV, mpps, page_size, num_pages, write_kv, err_flag);
 }
 
-extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool, void* v_pool, const int* page_table,
-                                      const int* tok_seq, const int* tok_pos, const int* seq_slot, const float* q_gain,
-                                      const float* k_gain, float eps, const float* rope_table, int rope_rows, int rot,
-                                      int tokens, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
-                                      int write_kv, int dtype, int* err_flag, cudaStream_t stream) {
+// pairs: the rotation turns neighbouring elements (2i, 2i + 1) instead of elements half a rotated part apart
+static int qk_norm_rope_append_go(const void* qkv, void* q_out, void* k_pool, void* v_pool, const int* page_table,
+                                  const int* tok_seq, const int* tok_pos, const int* seq_slot, const float* q_gain,
+                                  const float* k_gain, float eps, const float* rope_table, int rope_rows, int rot,
+                                  int tokens, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
+                                  int write_kv, int pairs, int dtype, int* err_flag, cudaStream_t stream) {
     if (tokens == 0) return 0;
     // H or KV may be 0 (only queries, or only keys and values); without kv heads nothing is appended
     RI_REQUIRE(tokens > 0 && H >= 0 && KV >= 0 && H + KV > 0 && Dh > 0, "qk_norm_rope_append: bad sizes");
@@ -354,7 +357,7 @@ extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool
     if ((long long)tokens * head_blocks > 4096) head_blocks = 1 > 4096 / tokens ? 1 : 4096 / tokens;
     RI_REQUIRE(tokens <= 2147483647 && head_blocks <= 65535, "qk_norm_rope_append: bad grid");
     dim3 grid(tokens, head_blocks);
-    const bool whole = !rope_table || rot == Dh;
+    const bool whole = !rope_table || (rot == Dh && !pairs);
     const bool aligned = ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 31) == 0);
     if (whole && aligned && (Dh == 64 || Dh == 128 || Dh == 256) && (dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16)) {
 #define RI_ROPE_VEC(T, V) launch_rope_vec<T, V>(grid, stream, qkv, q_out, k_pool, v_pool, page_table, tok_seq, tok_pos, \
@@ -386,14 +389,34 @@ extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool
         ri_launch_pdl(qk_norm_rope_append_kernel<float>, grid, dim3(32 * RK_WARPS), 0, stream,
             (const float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, page_table, tok_seq, tok_pos, seq_slot,
             q_gain, k_gain, eps, (const float2*)rope_table, rope_rows, rot, H, KV, Dh, mpps, page_size, num_pages,
-            write_kv, err_flag);
+            write_kv, pairs, err_flag);
     else if (dtype == RI_DTYPE_BF16)
         ri_launch_pdl(qk_norm_rope_append_kernel<__nv_bfloat16>, grid, dim3(32 * RK_WARPS), 0, stream,
             (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
             page_table, tok_seq, tok_pos, seq_slot, q_gain, k_gain, eps, (const float2*)rope_table, rope_rows, rot, H,
-            KV, Dh, mpps, page_size, num_pages, write_kv, err_flag);
+            KV, Dh, mpps, page_size, num_pages, write_kv, pairs, err_flag);
     else
         RI_FAIL(-1, "qk_norm_rope_append: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("qk_norm_rope_append");
     return 0;
+}
+
+extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool, void* v_pool, const int* page_table,
+                                      const int* tok_seq, const int* tok_pos, const int* seq_slot, const float* q_gain,
+                                      const float* k_gain, float eps, const float* rope_table, int rope_rows, int rot,
+                                      int tokens, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
+                                      int write_kv, int dtype, int* err_flag, cudaStream_t stream) {
+    return qk_norm_rope_append_go(qkv, q_out, k_pool, v_pool, page_table, tok_seq, tok_pos, seq_slot, q_gain, k_gain, eps,
+                                  rope_table, rope_rows, rot, tokens, H, KV, Dh, mpps, page_size, num_pages, write_kv, 0,
+                                  dtype, err_flag, stream);
+}
+
+extern "C" int ri_qk_norm_rope_append_pairs(const void* qkv, void* q_out, void* k_pool, void* v_pool, const int* page_table,
+                                            const int* tok_seq, const int* tok_pos, const int* seq_slot, const float* q_gain,
+                                            const float* k_gain, float eps, const float* rope_table, int rope_rows, int rot,
+                                            int tokens, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
+                                            int write_kv, int pairs, int dtype, int* err_flag, cudaStream_t stream) {
+    return qk_norm_rope_append_go(qkv, q_out, k_pool, v_pool, page_table, tok_seq, tok_pos, seq_slot, q_gain, k_gain, eps,
+                                  rope_table, rope_rows, rot, tokens, H, KV, Dh, mpps, page_size, num_pages, write_kv, pairs,
+                                  dtype, err_flag, stream);
 }

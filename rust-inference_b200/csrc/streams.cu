@@ -24,17 +24,21 @@ __global__ void __launch_bounds__(512)
 stream_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ mix,
                    const float* __restrict__ outw, const float* __restrict__ read, const int* __restrict__ rows,
                    const float* __restrict__ gain, T* __restrict__ out, int streams, int dim, float eps, int kind,
-                   int write_back) {
+                   int write_back, const T* __restrict__ delta2, const float* __restrict__ outw2,
+                   const T* __restrict__ delta3, const float* __restrict__ outw3, const float* __restrict__ bias) {
     constexpr int SN_CAP = NS ? NS : SN_MAX_STREAMS;
     const int S = NS ? NS : streams;
     extern __shared__ float sn_row[];                 // [dim]
     __shared__ float red[33];
     __shared__ float s_mix[SN_MAX_STREAMS * SN_MAX_STREAMS], s_out[SN_MAX_STREAMS], s_read[SN_MAX_STREAMS];
+    __shared__ float s_out2[SN_MAX_STREAMS], s_out3[SN_MAX_STREAMS];
     pdl_trigger();
     // the connection weights are parameters: read before the wait for the kernel in front
     for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[i] = mix ? mix[i] : (i / S == i % S ? 1.0f : 0.0f);
     for (int i = threadIdx.x; i < S; i += blockDim.x) {
         s_out[i] = outw ? outw[i] : 1.0f;
+        s_out2[i] = outw2 ? outw2[i] : 1.0f;
+        s_out3[i] = outw3 ? outw3[i] : 1.0f;
         s_read[i] = read ? read[i] : 1.0f;
     }
     pdl_wait();
@@ -42,6 +46,8 @@ stream_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const
     const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
     float* rp = resid + r * S * dim;
     const T* dp = delta ? delta + r * dim : nullptr;
+    const T* dp2 = (delta && delta2) ? delta2 + r * dim : nullptr;
+    const T* dp3 = (delta && delta3) ? delta3 + r * dim : nullptr;
     float sum = 0.0f;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
         float x[SN_CAP];
@@ -51,6 +57,8 @@ stream_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const
         float u = 0.0f;
         if (dp) {
             const float y = ld_f(dp + i);
+            const float y2 = dp2 ? ld_f(dp2 + i) : 0.0f;
+            const float y3 = dp3 ? ld_f(dp3 + i) : 0.0f;
 #pragma unroll
             for (int t = 0; t < SN_CAP; t++)
                 if (t < S) {
@@ -59,6 +67,8 @@ stream_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const
                     for (int s = 0; s < SN_CAP; s++)
                         if (s < S) a = fmaf(s_mix[s * S + t], x[s], a);
                     a = fmaf(s_out[t], y, a);
+                    if (dp2) a = fmaf(s_out2[t], y2, a);
+                    if (dp3) a = fmaf(s_out3[t], y3, a);
                     if (write_back) rp[(size_t)t * dim + i] = a;
                     u = fmaf(s_read[t], a, u);
                 }
@@ -84,7 +94,8 @@ stream_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const
         inv = 1.0f / sqrtf(total / (float)dim + eps);
     }
     T* op = out + (size_t)blockIdx.x * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(op + i, (sn_row[i] - mean) * inv * gain[i]);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        st_f(op + i, (sn_row[i] - mean) * inv * gain[i] + (bias ? bias[i] : 0.0f));
 }
 
 // The same for rows whose length is a multiple of 4 (and 16-byte aligned data): four neighbouring elements per
@@ -110,14 +121,18 @@ template <typename T, int NS>
 __global__ void __launch_bounds__(512)
 stream_norm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ mix,
                        const float* __restrict__ outw, const float* __restrict__ read, const int* __restrict__ rows,
-                       const float* __restrict__ gain, T* __restrict__ out, int dim, float eps, int kind, int write_back) {
+                       const float* __restrict__ gain, T* __restrict__ out, int dim, float eps, int kind, int write_back,
+                       const T* __restrict__ delta2, const float* __restrict__ outw2, const T* __restrict__ delta3,
+                       const float* __restrict__ outw3, const float* __restrict__ bias) {
     extern __shared__ __align__(16) float sn_row[];                 // [dim]
     __shared__ float red[33];
-    __shared__ float s_mix[NS * NS], s_out[NS], s_read[NS];
+    __shared__ float s_mix[NS * NS], s_out[NS], s_read[NS], s_out2[NS], s_out3[NS];
     pdl_trigger();
     for (int i = threadIdx.x; i < NS * NS; i += blockDim.x) s_mix[i] = mix ? mix[i] : (i / NS == i % NS ? 1.0f : 0.0f);
     for (int i = threadIdx.x; i < NS; i += blockDim.x) {
         s_out[i] = outw ? outw[i] : 1.0f;
+        s_out2[i] = outw2 ? outw2[i] : 1.0f;
+        s_out3[i] = outw3 ? outw3[i] : 1.0f;
         s_read[i] = read ? read[i] : 1.0f;
     }
     const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
@@ -125,6 +140,8 @@ stream_norm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, c
     __syncthreads();
     float* rp = resid + r * NS * dim;
     const T* dp = delta ? delta + r * dim : nullptr;
+    const T* dp2 = (delta && delta2) ? delta2 + r * dim : nullptr;
+    const T* dp3 = (delta && delta3) ? delta3 + r * dim : nullptr;
     const int nvec = dim >> 2;
     float sum = 0.0f;
     for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
@@ -138,6 +155,12 @@ stream_norm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, c
         if (dp) {
             const float4 yv = sn_ld4(dp + 4 * i);
             const float y[4] = {yv.x, yv.y, yv.z, yv.w};
+            float4 yv2 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (dp2) yv2 = sn_ld4(dp2 + 4 * i);
+            const float y2[4] = {yv2.x, yv2.y, yv2.z, yv2.w};
+            float4 yv3 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (dp3) yv3 = sn_ld4(dp3 + 4 * i);
+            const float y3[4] = {yv3.x, yv3.y, yv3.z, yv3.w};
 #pragma unroll
             for (int t = 0; t < NS; t++) {
                 float a[4];
@@ -147,6 +170,8 @@ stream_norm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, c
 #pragma unroll
                     for (int s = 0; s < NS; s++) a[e] = fmaf(s_mix[s * NS + t], x[s][e], a[e]);
                     a[e] = fmaf(s_out[t], y[e], a[e]);
+                    if (dp2) a[e] = fmaf(s_out2[t], y2[e], a[e]);
+                    if (dp3) a[e] = fmaf(s_out3[t], y3[e], a[e]);
                     u[e] = fmaf(s_read[t], a[e], u[e]);
                 }
                 if (write_back) sn_st4(rp + (size_t)t * dim + 4 * i, make_float4(a[0], a[1], a[2], a[3]));
@@ -179,14 +204,19 @@ stream_norm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, c
     for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
         const float4 v = *reinterpret_cast<const float4*>(sn_row + 4 * i);
         const float4 g = sn_ld4(gain + 4 * i);
-        sn_st4(op + 4 * i, make_float4((v.x - mean) * inv * g.x, (v.y - mean) * inv * g.y, (v.z - mean) * inv * g.z,
-                                       (v.w - mean) * inv * g.w));
+        float4 bb = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (bias) bb = sn_ld4(bias + 4 * i);
+        sn_st4(op + 4 * i, make_float4((v.x - mean) * inv * g.x + bb.x, (v.y - mean) * inv * g.y + bb.y,
+                                       (v.z - mean) * inv * g.z + bb.z, (v.w - mean) * inv * g.w + bb.w));
     }
 }
 
-extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix, const float* outw, const float* read,
-                              const int* rows, const float* gain, void* out, int n_rows, int streams, int dim, float eps,
-                              int kind, int dtype, cudaStream_t stream) {
+// delta2, outw2 and delta3, outw3: further pending outputs that join in the same pass (x_t += outw2[t] delta2 + outw3[t]
+// delta3, in this order after the first); bias: added to the normed row (a layer norm with a bias).  Each may be null.
+extern "C" int ri_stream_norm2(float* resid, const void* delta, const float* mix, const float* outw, const float* read,
+                               const int* rows, const float* gain, void* out, const void* delta2, const float* outw2,
+                               const void* delta3, const float* outw3, const float* bias, int n_rows, int streams, int dim, float eps, int kind, int dtype,
+                               cudaStream_t stream) {
     if (n_rows == 0) return 0;
     RI_REQUIRE(n_rows > 0 && dim > 0, "stream_norm: bad sizes rows=%d dim=%d", n_rows, dim);
     RI_REQUIRE(streams >= 1 && streams <= SN_MAX_STREAMS, "stream_norm: %d streams (1 to %d are built)", streams, SN_MAX_STREAMS);
@@ -197,8 +227,9 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
     const int write_back = rows ? 0 : 1;
     // rows of whole float4s at aligned addresses, up to 8 streams: the vector kernel
     const int unit = dtype == RI_DTYPE_F32 ? 15 : 7;
-    const bool vec = dim % 4 == 0 && streams <= 8 && (((uintptr_t)resid | (uintptr_t)gain) & 15) == 0 &&
-                     (((uintptr_t)delta | (uintptr_t)out) & unit) == 0;
+    RI_REQUIRE((delta || !delta2) && (delta2 || !delta3), "stream_norm: pending outputs are given first, second, third");
+    const bool vec = dim % 4 == 0 && streams <= 8 && (((uintptr_t)resid | (uintptr_t)gain | (uintptr_t)bias) & 15) == 0 &&
+                     (((uintptr_t)delta | (uintptr_t)delta2 | (uintptr_t)delta3 | (uintptr_t)out) & unit) == 0;
     if (vec) {
         const int nvec = dim / 4;
         // by the row length alone: the order of a row's additions must not depend on how many rows the step has
@@ -212,7 +243,8 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
             e = cudaFuncSetAttribute(stream_norm_vec_kernel<T, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) RI_FAIL((int)e, "stream_norm: %s", cudaGetErrorString(e));                                 \
         ri_launch_pdl(stream_norm_vec_kernel<T, NS>, dim3(n_rows), dim3(threads), smem, stream, resid, (const T*)delta,   \
-                      mix, outw, read, rows, gain, (T*)out, dim, eps, kind, write_back);                                 \
+                      mix, outw, read, rows, gain, (T*)out, dim, eps, kind, write_back, (const T*)delta2, outw2,        \
+                      (const T*)delta3, outw3, bias);                                                                    \
     } while (0)
 #define SN_GO(T, NS)                                                                                                     \
     do {                                                                                                                 \
@@ -224,7 +256,8 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
             e = cudaFuncSetAttribute(stream_norm_kernel<T, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         if (e != cudaSuccess) RI_FAIL((int)e, "stream_norm: %s", cudaGetErrorString(e));                                 \
         ri_launch_pdl(stream_norm_kernel<T, NS>, dim3(n_rows), dim3(threads), smem, stream, resid, (const T*)delta, mix,  \
-                      outw, read, rows, gain, (T*)out, streams, dim, eps, kind, write_back);                             \
+                      outw, read, rows, gain, (T*)out, streams, dim, eps, kind, write_back, (const T*)delta2, outw2,     \
+                      (const T*)delta3, outw3, bias);                                                                    \
     } while (0)
 #define SN_BY_STREAMS(T)                                                                                                 \
     switch (streams) {                                                                                                   \
@@ -245,4 +278,11 @@ extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix,
 #undef SN_VEC
     RI_CHECK_LAUNCH("stream_norm");
     return 0;
+}
+
+extern "C" int ri_stream_norm(float* resid, const void* delta, const float* mix, const float* outw, const float* read,
+                              const int* rows, const float* gain, void* out, int n_rows, int streams, int dim, float eps,
+                              int kind, int dtype, cudaStream_t stream) {
+    return ri_stream_norm2(resid, delta, mix, outw, read, rows, gain, out, nullptr, nullptr, nullptr, nullptr, nullptr, n_rows, streams, dim,
+                           eps, kind, dtype, stream);
 }

@@ -29,9 +29,11 @@ def compute_dtype(name) -> torch.dtype:
         raise ValueError(f"dtype must be bfloat16 or float32, got {name!r}") from None
 
 
-def _end_name(full_weight_name: str, local: str) -> str:
+def _end_name(full_weight_name: str, local: str, named=()) -> str:
     """The tensor name of an embedding's or a head's tensor: "weight" carries the given name itself,
-    any other tensor the same name with "weight" replaced by its own."""
+    any other tensor the same name with "weight" replaced by its own, unless the spec names it (``named``)."""
+    if local in dict(named):
+        return dict(named)[local]
     if local == "weight":
         return full_weight_name
     stem = full_weight_name[:-len("weight")] if full_weight_name.endswith("weight") else full_weight_name + "."
@@ -42,7 +44,7 @@ def _part_tensors(spec):
     """Yield (full tensor name, ParamInfo, owner key, local name) for every tensor of the model."""
     emb = spec.embedding_record()
     for local, info in part_class("embedding", emb).param_infos(emb).items():
-        yield _end_name(spec.embedding_name, local), info, ("embedding",), local
+        yield _end_name(spec.embedding_name, local, spec.end_names), info, ("embedding",), local
     for local, info in part_class("norm", spec.final_norm).param_infos(spec.final_norm).items():
         yield spec.final_norm_prefix + local, info, ("final_norm",), local
     for i, layer in enumerate(spec.layers):
@@ -53,7 +55,7 @@ def _part_tensors(spec):
     for local, info in part_class("head", head).param_infos(head).items():
         if local == "weight" and spec.tie_embeddings:
             continue                                   # the embedding's table
-        yield _end_name(spec.head_name, local), info, ("head",), local
+        yield _end_name(spec.head_name, local, spec.end_names), info, ("head",), local
 
 
 def expected_tensors(spec) -> Dict[str, ParamInfo]:
@@ -71,6 +73,8 @@ class Model:
         self.head_part = build_part("head", spec.head_record(), self.env)
         self.config = None
         self.cache_entry_layers = spec.cache_entries()
+        # an embedding that keeps state per sequence has a cache entry of its own, after the layers' entries
+        self.embed_cache_entry = len(self.cache_entry_layers) if self._embed_request() is not None else None
 
     # the two big tables, as the tests and the bench look at them
     @property
@@ -83,7 +87,7 @@ class Model:
 
     # ---- weights -------------------------------------------------------------------------
     def _to_role(self, t: torch.Tensor, role: str) -> torch.Tensor:
-        want = {"matrix": self.env.dtype, "gain": torch.float32, "table": torch.int32}[role]
+        want = {"matrix": self.env.dtype, "gain": torch.float32, "vector": torch.float32, "table": torch.int32}[role]
         return t.to(device=self.env.device, dtype=want).contiguous()
 
     def load_tensors(self, get) -> None:
@@ -151,8 +155,15 @@ class Model:
         return model
 
     # ---- what the cache has to hold -----------------------------------------------------------
+    def _embed_request(self):
+        ask = getattr(self.embed_part, "cache_request", None)
+        return ask() if ask is not None else None
+
     def cache_requests(self):
-        return [self.blocks[layer].mixer.cache_request() for layer in self.cache_entry_layers]
+        reqs = [self.blocks[layer].mixer.cache_request() for layer in self.cache_entry_layers]
+        if self.embed_cache_entry is not None:
+            reqs.append(self._embed_request())
+        return reqs
 
     @property
     def graph_safe(self) -> bool:
@@ -178,7 +189,10 @@ class Model:
     def forward(self, ids: torch.Tensor, ctx, cache, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """float32 logits [wanted rows, vocab] for the packed tokens ``ids``."""
         with section("embedding"):
-            resid = self.embed_part(ids, ctx)
+            if self.embed_cache_entry is not None:
+                resid = self.embed_part(ids, ctx, cache.layer(self.embed_cache_entry))
+            else:
+                resid = self.embed_part(ids, ctx)
         delta = None
         for e in self.spec.schedule:
             resid, delta = self.blocks[e.layer](resid, delta, ctx, cache.layer(e.cache, e.writes))

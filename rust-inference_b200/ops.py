@@ -27,6 +27,17 @@ _SIGNATURES = {
     ("elementwise", "ri_activation"): [_P, _P, _L, _I, _I, _P],
     ("elementwise", "ri_gate_heads"): [_P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     ("streams", "ri_stream_norm"): [_P] * 8 + [_I, _I, _I, _F, _I, _I, _P],
+    ("streams", "ri_stream_norm2"): [_P] * 13 + [_I, _I, _I, _F, _I, _I, _P],
+    ("pair_embedding", "ri_embed_pair_hash"): [_P] * 9 + [_I, _I, _I, _I, _I, _L, _L, _I, _I, _P, _P],
+    ("delta_rule", "ri_short_conv"): [_P, _L, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    ("delta_rule", "ri_delta_rule_recurrent"): [_P, _I, _I, _I, _I, _P, _L, _I, _P, _P, _P, _F, _P, _P, _P, _P] + [_I] * 7 + [_P],
+    ("elementwise", "ri_gated_act"): [_P, _P, _I, _I, _I, _I, _F, _F, _I, _P],
+    ("elementwise", "ri_scale_f32"): [_P, _L, _F, _P],
+    ("moe", "ri_moe_route"): [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    ("moe", "ri_moe_plan"): [_P, _P, _P, _P, _I, _I, _I, _P],
+    ("moe", "ri_moe_grouped_linear"): [_P, _L, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    ("moe", "ri_moe_combine"): [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    ("rope_kv", "ri_qk_norm_rope_append_pairs"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 10 + [_P, _P],
     ("latent_attention", "ri_latent_prep"): [_P, _L, _I, _I] + [_P] * 8 + [_F, _P] + [_I] * 11 + [_P, _P],
     ("gla", "ri_gla_recurrent"): [_P, _L, _I, _I, _I, _P, _P, _F, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     ("gla", "ri_gla_head_norm_gate"): [_P, _P, _F, _P, _L, _P, _I, _I, _I, _I, _I, _P],
@@ -211,8 +222,11 @@ NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
 def stream_norm(resid: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype, kind: str = "layernorm",
                 delta: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
                 out_w: Optional[torch.Tensor] = None, read: Optional[torch.Tensor] = None,
-                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                rows: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, more=()) -> torch.Tensor:
     """The norm in front of a sublayer over a residual of S streams ``resid`` [n, S, dim] (float32).
+
+    ``bias`` [dim] (float32) is added to the normed row.  ``more``: up to two further pending outputs as pairs
+    (tensor [n, dim], weights [S] or None for ones), added like ``delta`` with ``out_w``, in this order, in float32.
 
     First the pending update: with ``delta`` [n, dim] (the output of the sublayer before, compute dtype) every
     stream t becomes sum_s mix[s, t] x_s + out_w[t] delta (``mix`` absent: the identity; ``out_w`` absent: ones),
@@ -233,8 +247,19 @@ def stream_norm(resid: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: 
         _need(rows, "rows", torch.int32)
     n_out = n if rows is None else rows.numel()
     out = torch.empty((n_out, dim), dtype=out_dtype, device=resid.device)
-    _call("streams", "ri_stream_norm", resid.data_ptr(), _ptr(delta), _ptr(mix), _ptr(out_w), _ptr(read), _ptr(rows),
-          gain.data_ptr(), out.data_ptr(), n_out, S, dim, float(eps), NORM_KINDS[kind], _code(out_dtype), _stream())
+    more = list(more)
+    if len(more) > 2 or (more and delta is None):
+        raise KernelError("stream_norm: at most three pending outputs, the first of them in ``delta``")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (dim,))
+    for y, w in more:
+        _need(y, "pending output", out_dtype, (n, dim))
+        if w is not None:
+            _need(w, "weights of a pending output", torch.float32, (S,))
+    more += [(None, None)] * (2 - len(more))
+    _call("streams", "ri_stream_norm2", resid.data_ptr(), _ptr(delta), _ptr(mix), _ptr(out_w), _ptr(read), _ptr(rows),
+          gain.data_ptr(), out.data_ptr(), _ptr(more[0][0]), _ptr(more[0][1]), _ptr(more[1][0]), _ptr(more[1][1]), _ptr(bias),
+          n_out, S, dim, float(eps), NORM_KINDS[kind], _code(out_dtype), _stream())
     return out
 
 
@@ -578,9 +603,10 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
                         rope_table: Optional[torch.Tensor], rotary_dim: int,
                         k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                         tok_seq: torch.Tensor, tok_pos: torch.Tensor, seq_slot: torch.Tensor,
-                        write_kv: bool = True) -> torch.Tensor:
+                        write_kv: bool = True, pairs: bool = False) -> torch.Tensor:
     """Norm and rotate the q and k heads of ``qkv`` [tokens, (H+2KV)*Dh], append k
-    and v to the pools [pages, KV, page_size, Dh]; returns q [tokens, H, Dh]."""
+    and v to the pools [pages, KV, page_size, Dh]; returns q [tokens, H, Dh].  ``pairs``: the
+    rotation turns neighbouring elements (2i, 2i+1) instead of elements half a rotated part apart."""
     _need(qkv, "qkv")
     tokens = qkv.shape[0]
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
@@ -610,12 +636,20 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
             raise KernelError(f"rope table must be [positions, {rotary_dim // 2}, 2], got {tuple(rope_table.shape)}")
         rope_rows = rope_table.shape[0]
     q = torch.empty((tokens, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
-    _call("rope_kv", "ri_qk_norm_rope_append", qkv.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+    _call("rope_kv", "ri_qk_norm_rope_append_pairs", qkv.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           page_table.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_slot.data_ptr(), _ptr(q_gain),
           _ptr(k_gain), float(eps), _ptr(rope_table), rope_rows, rotary_dim, tokens, num_heads, num_kv_heads,
-          head_dim, page_table.shape[1], page_size, pages, 1 if write_kv else 0, _code(qkv.dtype),
+          head_dim, page_table.shape[1], page_size, pages, 1 if write_kv else 0, 1 if pairs else 0, _code(qkv.dtype),
           error_flag(qkv.device).data_ptr(), _stream())
     return q
+
+
+def _mask(window: int, chunk: int) -> int:
+    """The kernels' one mask integer: a window of the last ``window`` keys, or (negative) chunks of ``chunk``
+    positions counted from the sequence's start, of which a query sees its own up to itself."""
+    if window < 0 or chunk < 0 or (window and chunk):
+        raise KernelError(f"attention: window {window} and chunk {chunk}: at most one of them, none negative")
+    return int(window) if window else -int(chunk)
 
 
 def _sink(sink: Optional[torch.Tensor], heads: int) -> Optional[int]:
@@ -627,7 +661,7 @@ def _sink(sink: Optional[torch.Tensor], heads: int) -> Optional[int]:
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               seq_slot: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_new: int, scale: float,
-              window: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+              window: int = 0, sink: Optional[torch.Tensor] = None, chunk: int = 0) -> torch.Tensor:
     """Causal attention of the step's new tokens (q [tokens, H, Dh], sequences back to back as
     ``seq_start`` says) over the paged cache, which already holds their keys and values: float32 or
     bfloat16, any head size up to 512, any page size.  Every (token, head) is computed in one fixed
@@ -649,7 +683,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     out = torch.empty_like(q)
     _call("attention_rows", "ri_attention_rows", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
           page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(), seqs, int(max_new),
-          H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window), _sink(sink, H), _code(q.dtype),
+          H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), _mask(window, chunk), _sink(sink, H), _code(q.dtype),
           error_flag(q.device).data_ptr(), _stream())
     return out
 
@@ -667,7 +701,7 @@ def _decode_parts(head_dim: int, chunks: int) -> int:
 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                      seq_slot: torch.Tensor, seq_len: torch.Tensor, scale: float, window: int,
-                     max_len: int, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     max_len: int, sink: Optional[torch.Tensor] = None, chunk: int = 0) -> torch.Tensor:
     """Attention of one new token per sequence (q [seqs, H, Dh], bfloat16) over the
     paged cache, keys split into chunks of ``DECODE_CHUNK``; ``max_len`` bounds the
     sequences' lengths after this step and sizes the scratch memory."""
@@ -691,13 +725,14 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     _call("attention_decode", "ri_attention_decode_sink", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), o_part.data_ptr(), ml_part.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(),
           seq_len.data_ptr(), seqs, H, KV, Dh, page_table.shape[1], page_size, pages, chunks, float(scale),
-          int(window), _sink(sink, H), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+          _mask(window, chunk), _sink(sink, H), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
     return out
 
 
 def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                       seq_slot: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_new: int,
-                      scale: float, window: int, sink: Optional[torch.Tensor] = None, v_dims: int = 0) -> torch.Tensor:
+                      scale: float, window: int, sink: Optional[torch.Tensor] = None, v_dims: int = 0,
+                      chunk: int = 0) -> torch.Tensor:
     """Attention of the step's new tokens (q [tokens, H, Dh], bfloat16, sequences back
     to back as ``seq_start`` says) over the paged cache, which already holds their keys
     and values; ``max_new`` is the most tokens one sequence brings.  ``v_pool`` may be ``k_pool``
@@ -718,7 +753,7 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
     _need(seq_len, "seq_len", torch.int32, (seqs,))
     out = torch.empty_like(q)
-    if Dh in TCGEN05_HEAD_DIMS and not _NO_TCGEN05 and sink is None:
+    if Dh in TCGEN05_HEAD_DIMS and not _NO_TCGEN05 and sink is None and not chunk:
         # head sizes of 64 and 128: the tcgen05 / tensor-memory kernel (it has no sink term: those go below)
         _call("attention_prefill_tc", "ri_attention_prefill_tc", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
               out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
@@ -727,7 +762,7 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
         return out
     _call("attention_prefill", "ri_attention_prefill", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
-          seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
+          seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), _mask(window, chunk),
           _sink(sink, H), int(v_dims), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
     return out
 
@@ -799,3 +834,200 @@ def mark_seen(seen: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor) -> N
     _need(tokens, "tokens", torch.int32, rows.shape)
     _call("sampling", "ri_mark_seen", seen.data_ptr(), seen.stride(0), rows.data_ptr(), tokens.data_ptr(),
           rows.numel(), seen.shape[1], _stream())
+
+
+# ---------------------------------------------------------------------------------------
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor in place (float32)."""
+    _need(x, "x", torch.float32)
+    if factor != 1.0:
+        _call("elementwise", "ri_scale_f32", x.data_ptr(), x.numel(), float(factor), _stream())
+    return x
+
+
+def embed_pair_hash(ids: torch.Tensor, table: torch.Tensor, pairs: torch.Tensor, last_token: torch.Tensor,
+                    tok_seq: torch.Tensor, tok_pos: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor,
+                    mul_prev: int, mul_cur: int, single: bool = False) -> torch.Tensor:
+    """float32 rows ``table[id] + pairs[(previous id * mul_prev + id * mul_cur) mod buckets]`` with ``pairs``
+    [buckets + 1, dim]; a sequence's first token (position 0) takes row ``buckets``.  The token before a step's first
+    one comes from ``last_token`` [slots] (int32), which is brought up to date.  ``single``: every sequence brings
+    one token (one launch instead of two)."""
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    _need(pairs, "pairs", table.dtype)
+    _need(last_token, "last_token", torch.int32)
+    tokens, (vocab, dim) = ids.numel(), table.shape
+    if pairs.dim() != 2 or pairs.shape[1] != dim or pairs.shape[0] < 2:
+        raise KernelError(f"embed_pair_hash: pair table {tuple(pairs.shape)} does not fit rows of {dim}")
+    seqs = seq_slot.numel()
+    for t, n in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (seq_slot, "seq_slot"), (seq_start, "seq_start")):
+        _need(t, n, torch.int32)
+    out = torch.empty((tokens, dim), dtype=torch.float32, device=table.device)
+    _call("pair_embedding", "ri_embed_pair_hash", ids.data_ptr(), table.data_ptr(), pairs.data_ptr(), out.data_ptr(),
+          last_token.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), tokens,
+          seqs, dim, vocab, pairs.shape[0] - 1, int(mul_prev), int(mul_cur), 1 if single else 0, _code(table.dtype),
+          error_flag(table.device).data_ptr(), _stream())
+    if not (single and tokens == seqs):
+        add_launches(1)
+    return out
+
+
+def short_conv(x: torch.Tensor, col0: int, weight: torch.Tensor, state: torch.Tensor, tok_seq: torch.Tensor,
+               seq_slot: torch.Tensor, seq_start: torch.Tensor, single: bool = False) -> torch.Tensor:
+    """Causal convolution over time per channel, then silu: channels are columns ``col0 .. col0 + C`` of ``x``
+    [tokens, N]; ``weight`` [C, taps] float32 (the last column is the current token's); ``state`` [slots, taps-1, C]
+    float32 holds every sequence's last inputs (zeros at its start) and is brought up to date.  float32 [tokens, C]."""
+    _need(x, "x")
+    _need(weight, "weight", torch.float32)
+    C, taps = weight.shape
+    tokens, ld = x.shape
+    if col0 < 0 or col0 + C > ld:
+        raise KernelError("short_conv: the channels lie outside the matrix")
+    _need(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != (taps - 1, C):
+        raise KernelError(f"short_conv: state {tuple(state.shape)} does not fit {taps} taps on {C} channels")
+    seqs = seq_slot.numel()
+    for t, n in ((tok_seq, "tok_seq"), (seq_slot, "seq_slot"), (seq_start, "seq_start")):
+        _need(t, n, torch.int32)
+    y = torch.empty((tokens, C), dtype=torch.float32, device=x.device)
+    _call("delta_rule", "ri_short_conv", x.data_ptr(), ld, int(col0), weight.data_ptr(), y.data_ptr(), state.data_ptr(),
+          tok_seq.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), tokens, seqs, C, taps, 1 if single else 0,
+          _code(x.dtype), _stream())
+    if not (single and tokens == seqs) and taps > 1:
+        add_launches(1)
+    return y
+
+
+def delta_rule_recurrent(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, proj: torch.Tensor, beta_col: int,
+                         z: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, qscale: float, state: torch.Tensor,
+                         seq_slot: torch.Tensor, seq_start: torch.Tensor, heads: int, qk_heads: int, dim: int, vdim: int,
+                         single: bool = False) -> torch.Tensor:
+    """The gated delta rule over the step's new tokens.  Per head h (with q/k head h // (heads // qk_heads)) the state S
+    [dim, vdim] (float32, in ``state`` [slots, H, dim, vdim], updated in place) goes
+    S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q, with q and k made unit vectors (q also times
+    ``qscale``), g = exp(-exp(a_log[h]) softplus(z + dt_bias)) per key channel and beta = sigmoid of column
+    ``beta_col + h`` of ``proj``.  ``qkv`` [tokens, C] float32 holds q, k, v from ``q_col``, ``k_col``, ``v_col``;
+    ``z`` [tokens, H*dim] in the compute dtype.  Returns o [tokens, H, vdim] float32."""
+    _need(qkv, "qkv", torch.float32)
+    tokens, C = qkv.shape
+    _need(proj, "proj")
+    _need(z, "z", proj.dtype, (tokens, heads * dim))
+    _need(dt_bias, "dt_bias", torch.float32, (heads * dim,))
+    _need(a_log, "a_log", torch.float32, (heads,))
+    _need(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError(f"delta_rule_recurrent: state {tuple(state.shape)} does not fit {heads} heads of {dim} x {vdim}")
+    if heads % qk_heads or max(q_col, k_col) + qk_heads * dim > C or v_col + heads * vdim > C or beta_col + heads > proj.shape[1]:
+        raise KernelError("delta_rule_recurrent: the columns do not fit the matrices")
+    seqs = seq_slot.numel()
+    _need(seq_slot, "seq_slot", torch.int32, (seqs,))
+    _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
+    o = torch.empty((tokens, heads, vdim), dtype=torch.float32, device=qkv.device)
+    _call("delta_rule", "ri_delta_rule_recurrent", qkv.data_ptr(), C, int(q_col), int(k_col), int(v_col), proj.data_ptr(),
+          proj.shape[1], int(beta_col), z.data_ptr(), dt_bias.data_ptr(), a_log.data_ptr(), float(qscale), state.data_ptr(),
+          o.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seqs, heads, qk_heads, dim, vdim,
+          1 if single and tokens == seqs else 0, _code(proj.dtype), _stream())
+    return o
+
+
+GATES = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+
+def gated_act(gate_up: torch.Tensor, kind: str, block: Optional[int] = None, limit: float = 0.0,
+              alpha: float = 1.0) -> torch.Tensor:
+    """f(gate) * up' for ``gate_up`` [rows, 2*inter] whose gate and up columns alternate in blocks of ``block``
+    channels (default: all gates, then all ups).  ``kind``: "silu", "gelu_tanh", or "clamped_swish":
+    g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    _need(gate_up, "gate_up")
+    if kind not in GATES:
+        raise KernelError(f"gate {kind!r} is not built (known: {', '.join(sorted(GATES))})")
+    rows, two = gate_up.shape
+    if two % 2:
+        raise KernelError("gated_act: the last dimension must be even")
+    inter = two // 2
+    block = inter if block is None else int(block)
+    out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _call("elementwise", "ri_gated_act", gate_up.data_ptr(), out.data_ptr(), rows, inter, block, GATES[kind], float(limit),
+          float(alpha), _code(gate_up.dtype), _stream())
+    return out
+
+
+def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, block: int, kind: str = "silu", limit: float = 0.0,
+                 alpha: float = 1.0) -> torch.Tensor:
+    """f(x Wg^T) * (x Wu^T)' for the stacked matrix of ``linear_swiglu``; "silu" takes that function's fused kernels,
+    the other gates (see ``gated_act``) run the product and the gate one after the other."""
+    if kind == "silu":
+        return linear_swiglu(x, w_gate_up, block)
+    return gated_act(linear(x, w_gate_up), kind, block, limit, alpha)
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: int):
+    """Per token the ``top`` router outputs with the largest softmax(router x) + correction (ties: the lower index),
+    and as weights their softmax scores divided by their sum (+ 1e-20).  ``router`` [N, D] and ``correction`` [N]
+    float32.  Returns (int32 [tokens, top], float32 [tokens, top])."""
+    _need(x, "x")
+    tokens, D = x.shape
+    _need(router, "router", torch.float32)
+    N = router.shape[0]
+    if router.shape[1] != D:
+        raise KernelError(f"moe_route: router {tuple(router.shape)} does not fit rows of {D}")
+    _need(correction, "correction", torch.float32, (N,))
+    idx = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+    weight = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+    _call("moe", "ri_moe_route", x.data_ptr(), router.data_ptr(), correction.data_ptr(), idx.data_ptr(), weight.data_ptr(),
+          tokens, D, N, int(top), _code(x.dtype), _stream())
+    return idx, weight
+
+
+def moe_plan(idx: torch.Tensor, experts: int):
+    """The step's (token, choice) pairs grouped by expert for the grouped products: (perm int32 [pairs], tiles int32
+    [max_tiles, 3] of (expert, first row, rows), meta int32 [2] = (tiles, rows)); choices >= ``experts`` are left out.
+    Everything stays on the device."""
+    _need(idx, "idx", torch.int32)
+    pairs = idx.numel()
+    _, lib = _fn("moe", "ri_moe_plan")
+    max_tiles = int(lib.ri_moe_max_tiles(int(pairs), int(experts)))
+    perm = torch.empty(max(pairs, 1), dtype=torch.int32, device=idx.device)
+    tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=idx.device)
+    meta = torch.empty(2, dtype=torch.int32, device=idx.device)
+    _call("moe", "ri_moe_plan", idx.data_ptr(), perm.data_ptr(), tiles.data_ptr(), meta.data_ptr(), pairs, int(experts),
+          max_tiles, _stream())
+    return perm, tiles, meta
+
+
+def moe_grouped_linear(a: torch.Tensor, w: torch.Tensor, plan, rows_out: int, gather_div: int = 0, scatter: bool = False,
+                       out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y[out(r)] = w[e] a[in(r)] for every row r of the plan's tiles; ``w`` [E, N, K]; in(r) = perm[r] // gather_div
+    (``gather_div`` > 0) or r; out(r) = perm[r] (``scatter``) or r.  Rows that no tile covers are not written."""
+    perm, tiles, meta = plan
+    _need(a, "a")
+    _need(w, "w", a.dtype)
+    E, N, K = w.shape
+    if a.dim() != 2 or a.shape[1] != K:
+        raise KernelError(f"moe_grouped_linear: a {tuple(a.shape)} and w {tuple(w.shape)} do not fit")
+    out_dtype = out_dtype or a.dtype
+    if out_dtype not in (a.dtype, torch.float32):
+        raise KernelError("moe_grouped_linear: the result is float32 or the compute dtype")
+    y = torch.empty((rows_out, N), dtype=out_dtype, device=a.device)
+    _call("moe", "ri_moe_grouped_linear", a.data_ptr(), a.stride(0), w.data_ptr(), y.data_ptr(), N, perm.data_ptr(),
+          tiles.data_ptr(), meta.data_ptr(), tiles.shape[0], N, K, int(gather_div), 1 if scatter else 0,
+          1 if out_dtype == torch.float32 else 0, _code(a.dtype), _stream())
+    return y
+
+
+def moe_combine(pair_out: torch.Tensor, idx: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, experts: int,
+                extra: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[t] = sum_j weight[t, j] * (idx[t, j] >= experts ? x[t] : pair_out[t * top + j]) (+ extra[t]), in float32, j
+    ascending, rounded once to x's dtype."""
+    _need(x, "x")
+    tokens, D = x.shape
+    top = idx.shape[1]
+    _need(pair_out, "pair_out", torch.float32, (tokens * top, D))
+    _need(idx, "idx", torch.int32, (tokens, top))
+    _need(weight, "weight", torch.float32, (tokens, top))
+    if extra is not None:
+        _need(extra, "extra", x.dtype, (tokens, D))
+    y = torch.empty_like(x)
+    _call("moe", "ri_moe_combine", pair_out.data_ptr(), idx.data_ptr(), weight.data_ptr(), x.data_ptr(), _ptr(extra),
+          y.data_ptr(), tokens, D, top, int(experts), _code(x.dtype), _stream())
+    return y

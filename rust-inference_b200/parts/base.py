@@ -78,26 +78,48 @@ class CacheRequest:
     """What a mixer needs stored per sequence.
 
     Keys and values: ``kv_heads`` x ``head_dim`` per token (0 for none), all of
-    them (``window`` 0) or the last ``window``.  ``shared_kv``: the values are the
-    keys (a latent that serves as both), so one pool is kept and handed out as both.
+    them (``window`` 0) or the last ``window``; ``chunk`` > 0 instead of a window: the
+    keys of the query's own chunk of that many positions, counted from the sequence's
+    start.  ``shared_kv``: the values are the keys (a latent that serves as both), so
+    one pool is kept and handed out as both.
     Fixed-size state: ``state_shape`` per sequence (empty for none), zeroed when a
-    slot is given out."""
+    slot is given out; ``more_state``: further such tensors as (shape, dtype) pairs,
+    handed out in this order as ``LayerCache.more_state``."""
     kv_heads: int = 0
     head_dim: int = 0
     window: int = 0
     state_shape: tuple = ()
     state_dtype: torch.dtype = torch.float32
     shared_kv: bool = False
+    chunk: int = 0
+    more_state: tuple = ()
+
+    @property
+    def mask(self) -> int:
+        """The one integer the kernels and the page bookkeeping take: the window, or minus the chunk size."""
+        if self.window and self.chunk:
+            raise ValueError("a cache entry has a window or a chunked mask, not both")
+        return self.window if self.window else -self.chunk
 
 
 @dataclass
 class Pending:
     """A sublayer's output that has not joined the residual yet, for a residual kept as several streams: the norm in
     front of the next sublayer applies x_t <- sum_s mix[s, t] x_s + out[t] y while it reads the streams
-    (``mix`` None: the identity; ``out`` None: ones)."""
+    (``mix`` None: the identity; ``out`` None: ones).  ``more``: further outputs that join in the same pass (a layer
+    whose mixer and feed-forward run side by side, a mixer that is a weighted sum of two), as pairs (tensor, weights
+    [streams] or None for ones): x_t <- ... + out[t] y + w2[t] y2 + ..., the sum taken in float32."""
     y: torch.Tensor
     mix: Optional[torch.Tensor] = None
     out: Optional[torch.Tensor] = None
+    more: tuple = ()
+
+
+@dataclass
+class WeightedSum:
+    """A part's output given as sum_i factor_i * tensor_i, the sum not yet taken: whoever adds it to the residual adds
+    the terms one by one in float32 (``parts/link.py``), so that no term is rounded a second time."""
+    terms: tuple                 # ((tensor, factor), ...)
 
 
 class Part:

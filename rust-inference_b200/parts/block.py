@@ -78,6 +78,26 @@ class StreamBlock(BlockBase):
         return resid, self.ffn_link.pending(self.ffn(x, ctx))
 
 
+@register_block("parallel")
+class ParallelBlock(BlockBase):
+    """One norm whose output the mixer and the feed-forward (optional) both read; their outputs join the residual
+    together, through the layer's connection (``parts/link.py``): x <- x + scale * (mixer(h) + ffn(h)) for a
+    connection without weights.  The sum is taken in float32 by the next norm, term by term."""
+
+    @classmethod
+    def slots(cls, spec):
+        out = [("norm", "norm", spec.norm), ("link", "link", spec.link), ("mixer", "mixer", spec.mixer)]
+        if spec.ffn is not None:
+            out.append(("ffn", "ffn", spec.ffn))
+        return tuple(out)
+
+    def __call__(self, resid, delta, ctx, cache):
+        x = self.norm(resid, delta, read=self.link.read)
+        a = self.mixer(x, ctx, cache)
+        f = self.ffn(x, ctx) if self.spec.ffn is not None else None
+        return resid, self.link.pending(a, f)
+
+
 def norm_before(norm, resid, delta, reader):
     """``norm(resid + delta)`` for the part ``reader``; a norm that takes hints is told which matrix is read next."""
     if norm.takes_hint:

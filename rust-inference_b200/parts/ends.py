@@ -22,7 +22,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Part
+from .base import CacheRequest, Part
 from .registry import ParamInfo, register_embedding, register_head
 
 
@@ -44,6 +44,33 @@ class TokenEmbedding(Part):
         return ops.embed(ids, self.table, getattr(self.spec, "scale", 1.0), getattr(self.spec, "copies", 1))
 
 
+@register_embedding("pair_hash")
+class PairHashEmbedding(Part):
+    """Token rows plus rows of a hashed table of (previous token, token) pairs; the previous token of a step's first
+    token is per-sequence state (one int32 per cache slot), which the part asks the cache for."""
+    graph_safe = True
+
+    @classmethod
+    def param_infos(cls, spec):
+        return {"weight": ParamInfo((spec.vocab_size, spec.hidden_size), "matrix"),
+                spec.pairs_name: ParamInfo((spec.buckets + 1, spec.hidden_size), "matrix")}
+
+    def load(self, tensors):
+        self.table = tensors["weight"]
+        self.pairs = tensors[self.spec.pairs_name]
+
+    def weight_bytes(self):
+        return (self.table.numel() + self.pairs.numel()) * self.table.element_size()
+
+    def cache_request(self):
+        return CacheRequest(state_shape=(1,), state_dtype=torch.int32)
+
+    def __call__(self, ids, ctx, cache):
+        s = self.spec
+        return ops.embed_pair_hash(ids, self.table, self.pairs, cache.state.view(-1), ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
+                                   ctx.seq_start, s.mul_prev, s.mul_cur, single=ctx.decode_only)
+
+
 @register_head("linear")
 class LinearHead(Part):
     graph_safe = True
@@ -62,4 +89,4 @@ class LinearHead(Part):
         return self.weight
 
     def __call__(self, x):
-        return ops.linear(x, self.weight, out_dtype=torch.float32)
+        return ops.scale_(ops.linear(x, self.weight, out_dtype=torch.float32), getattr(self.spec, "scale", 1.0))

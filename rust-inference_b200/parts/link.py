@@ -4,14 +4,21 @@
 the start; the model's final norm reads their sum).  A sublayer reads u = sum_s in[s] x_s, and its output y turns
 the streams, all at once from the old ones, into x_t <- sum_s mix[s, t] x_s + out[t] y (``mix`` is indexed
 [from, to]).  The three tensors ``in`` [S], ``out`` [S] and ``mix`` [S, S] stay float32.  A record with
-``learned`` False has no tensors and one stream: u = x and x <- x + y, the ordinary residual sum.
+``learned`` False has no tensors and one stream: u = x and x <- x + scale * y, the ordinary residual sum (with the
+record's constant ``scale``, 1 by default).
+
+Several outputs may join at once (``pending(a, b)``: a layer whose mixer and feed-forward read the same norm), and an
+output may itself be a weighted sum that has not been taken (:class:`~.base.WeightedSum`): every term is then added
+with out[t] times its factor, in float32, in the order given.
 
 The part computes nothing itself: the norm in front of the next sublayer does the update while it reads the streams
 (``ops.stream_norm``); this part holds the weights and wraps an output as :class:`~.base.Pending`.
 """
 from __future__ import annotations
 
-from .base import Part, Pending
+import torch
+
+from .base import Part, Pending, WeightedSum
 from .registry import ParamInfo, register_link
 
 
@@ -26,6 +33,7 @@ class HyperConnection(Part):
         if not spec.learned and spec.streams != 1:
             raise ValueError("a connection without weights is the plain residual sum and has one stream")
         self.read = self.mix = self.out = None
+        self._scaled = {}
 
     @classmethod
     def param_infos(cls, spec):
@@ -37,9 +45,34 @@ class HyperConnection(Part):
     def load(self, tensors):
         if self.spec.learned:
             self.read, self.out, self.mix = tensors["in"], tensors["out"], tensors["mix"].contiguous()
+            self._scaled = {}
 
     def weight_bytes(self):
         return 0 if self.read is None else 4 * (self.read.numel() + self.out.numel() + self.mix.numel())
 
-    def pending(self, y) -> Pending:
-        return Pending(y, self.mix, self.out)
+    def _out_times(self, factor: float):
+        """The weights out[t] * factor (float32 [streams]); None stands for ones."""
+        factor = float(factor) * float(getattr(self.spec, "scale", 1.0))
+        if factor == 1.0:
+            return self.out
+        w = self._scaled.get(factor)
+        if w is None:
+            if self.out is None:
+                w = torch.full((self.spec.streams,), factor, dtype=torch.float32, device=self.env.device)
+            else:
+                w = (self.out.double() * factor).float().contiguous()
+            self._scaled[factor] = w
+        return w
+
+    def pending(self, *outputs) -> Pending:
+        terms = []
+        for y in outputs:
+            if y is None:
+                continue
+            if isinstance(y, WeightedSum):
+                terms += [(t, self._out_times(f)) for t, f in y.terms]
+            else:
+                terms.append((y, self._out_times(1.0)))
+        if not terms:
+            raise ValueError("a sublayer without output")
+        return Pending(terms[0][0], self.mix, terms[0][1], tuple(terms[1:]))

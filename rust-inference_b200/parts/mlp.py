@@ -45,6 +45,46 @@ class SwiGLU(FeedForward):
             return ops.linear(z, self.down)
 
 
+@register_ffn("gated")
+class GatedFF(FeedForward):
+    """down(f(gate x) * up x), no biases, with the gate function a record field: "silu", "gelu_tanh", or
+    "clamped_swish" (g sigmoid(alpha g) (u + 1) with g = min(gate x, limit), u = clamp(up x, -limit, limit)).  The
+    tensors are "gate", "up", "down"; gate and up are stacked at load as for SwiGLU."""
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.gate not in ops.GATES:
+            raise ValueError(f"gate {spec.gate!r} is not built (known: {', '.join(sorted(ops.GATES))})")
+
+    @classmethod
+    def param_infos(cls, spec):
+        D, I = spec.hidden_size, spec.intermediate_size
+        return {"gate": ParamInfo((I, D)), "up": ParamInfo((I, D)), "down": ParamInfo((D, I))}
+
+    def load(self, tensors):
+        g, u = tensors["gate"], tensors["up"]
+        inter, width = g.shape
+        self.block = 8 if inter % 8 == 0 else inter
+        nb = inter // self.block
+        self.gate_up = torch.stack([g.view(nb, self.block, width), u.view(nb, self.block, width)], dim=1) \
+            .reshape(2 * inter, width).contiguous()
+        self.down = tensors["down"].contiguous()
+
+    def weight_bytes(self):
+        return (self.gate_up.numel() + self.down.numel()) * self.gate_up.element_size()
+
+    def reads_first(self):
+        return self.gate_up
+
+    def __call__(self, x, ctx):
+        s = self.spec
+        with section("mlp gate/up"):
+            z = ops.linear_gated(x, self.gate_up, self.block, s.gate, s.limit, s.alpha)
+        with section("mlp down"):
+            return ops.linear(z, self.down)
+
+
 @register_ffn("dense")
 class DenseFF(FeedForward):
     """down(act(up x)), no biases; the activation ("relu2": the square of relu, or "gelu_tanh") is a record field."""

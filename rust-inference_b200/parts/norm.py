@@ -3,8 +3,8 @@
 stream, adds the pending output of the previous part on the way if there is
 one, and writes the normed rows in the compute dtype.
 
-LayerNorm (no bias): y = (x - mean) / sqrt(var + eps) * gain with var the mean squared
-deviation, float32.  It reads a residual of one or several streams ([tokens, dim] or
+LayerNorm: y = (x - mean) / sqrt(var + eps) * gain (+ bias, where the record names one) with var
+the mean squared deviation, float32.  It reads a residual of one or several streams ([tokens, dim] or
 [tokens, streams, dim]): the pending output joins the streams by its connection's weights
 (:class:`~.base.Pending`) and the row that is normed is the streams' weighted sum (``read``;
 absent: their plain sum), all in the same kernel."""
@@ -43,21 +43,26 @@ class LayerNorm(Norm):
 
     @classmethod
     def param_infos(cls, spec):
-        return {spec.weight_name: ParamInfo((spec.size,), "gain")}
+        infos = {spec.weight_name: ParamInfo((spec.size,), "gain")}
+        if getattr(spec, "bias_name", ""):
+            infos[spec.bias_name] = ParamInfo((spec.size,), "vector")
+        return infos
 
     def load(self, tensors):
         self.gain = tensors[self.spec.weight_name]
+        self.bias = tensors[self.spec.bias_name] if getattr(self.spec, "bias_name", "") else None
 
     def weight_bytes(self):
-        return self.gain.numel() * 4
+        return self.gain.numel() * 4 * (1 if getattr(self, "bias", None) is None else 2)
 
     def __call__(self, resid, delta=None, rows=None, then=None, read=None):
         streams = resid if resid.dim() == 3 else resid.view(resid.shape[0], 1, resid.shape[1])
         y = mix = out = None
+        more = ()
         if isinstance(delta, Pending):
-            y, mix, out = delta.y, delta.mix, delta.out
+            y, mix, out, more = delta.y, delta.mix, delta.out, delta.more
         elif delta is not None:
             y = delta
         with section("layernorm"):
             return ops.stream_norm(streams, self.gain, self.spec.eps, self.env.dtype, "layernorm", delta=y, mix=mix,
-                                   out_w=out, read=read, rows=rows)
+                                   out_w=out, read=read, rows=rows, bias=self.bias, more=more)

@@ -25,6 +25,7 @@ class ParamInfo:
 
     role "matrix": kept in the compute dtype, random init N(0, 0.02);
     role "gain":   kept in float32, random init 1 + U(-0.1, 0.1);
+    role "vector": kept in float32, random init N(0, 0.02) (biases, rates, small weights that enter float32 arithmetic);
     role "table":  integer table, kept as int32, random init zeros.
     """
     shape: Tuple[int, ...]

@@ -70,7 +70,7 @@ def random_tensor(seed: int, name: str, shape, role: str, dtype: torch.dtype, de
     shape = tuple(int(d) for d in shape)
     if role == "table":
         return torch.zeros(shape, dtype=torch.int32, device=device)
-    if role not in ("matrix", "gain"):
+    if role not in ("matrix", "gain", "vector"):
         raise ValueError(f"unknown parameter role {role!r}")
     if dtype not in (torch.float32, torch.bfloat16):
         raise ValueError(f"random weights are float32 or bfloat16, not {dtype}")
@@ -78,7 +78,7 @@ def random_tensor(seed: int, name: str, shape, role: str, dtype: torch.dtype, de
     row = 1
     for d in shape[1:]:
         row *= d
-    if role == "matrix":
+    if role in ("matrix", "vector"):
         _fill(out, tensor_key(seed, name), first_row * row, 0, MATRIX_STD, 0.0)
     else:
         _fill(out, tensor_key(seed, name), first_row * row, 1, 1.0, GAIN_SPREAD)

@@ -14,7 +14,8 @@ import torch
 
 __all__ = ["embed", "rmsnorm", "add_rows", "silu_mul", "linear_swiglu", "linear", "qk_norm_rope_append", "attention", "argmax",
            "sample", "mark_seen", "stream_norm", "activation", "gate_heads", "linear_heads", "latent_prep", "gla_recurrent",
-           "head_norm_gate", "linear_act"]
+           "head_norm_gate", "linear_act", "scale_", "embed_pair_hash", "short_conv", "delta_rule_recurrent", "gated_act",
+           "linear_gated", "moe_route", "moe_plan", "moe_grouped_linear", "moe_combine"]
 
 
 def embed(ids, table, scale=1.0, copies=1):
@@ -22,23 +23,27 @@ def embed(ids, table, scale=1.0, copies=1):
     return x if copies == 1 else x[:, None, :].repeat(1, copies, 1)
 
 
-def stream_norm(resid, gain, eps, out_dtype, kind="layernorm", delta=None, mix=None, out_w=None, read=None, rows=None):
+def stream_norm(resid, gain, eps, out_dtype, kind="layernorm", delta=None, mix=None, out_w=None, read=None, rows=None,
+                bias=None, more=()):
     n, S, dim = resid.shape
     x = resid if rows is None else resid[rows.long()]
     if delta is not None:
-        y = (delta if rows is None else delta[rows.long()]).float()
         m = torch.eye(S) if mix is None else mix
-        o = torch.ones(S) if out_w is None else out_w
-        x = torch.einsum("st,nsd->ntd", m, x) + o[None, :, None] * y[:, None, :]
+        x = torch.einsum("st,nsd->ntd", m, x)
+        for y, w in [(delta, out_w)] + list(more):
+            y = (y if rows is None else y[rows.long()]).float()
+            o = torch.ones(S) if w is None else w
+            x = x + o[None, :, None] * y[:, None, :]
         if rows is None:
             resid.copy_(x)
     r = torch.ones(S) if read is None else read
     u = torch.einsum("s,nsd->nd", r, x)
+    b = 0.0 if bias is None else bias
     if kind == "layernorm":
         mu = u.mean(-1, keepdim=True)
         var = ((u - mu) ** 2).mean(-1, keepdim=True)
-        return ((u - mu) / torch.sqrt(var + eps) * gain).to(out_dtype)
-    return (u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * gain).to(out_dtype)
+        return ((u - mu) / torch.sqrt(var + eps) * gain + b).to(out_dtype)
+    return (u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * gain + b).to(out_dtype)
 
 
 def activation(x, kind):
@@ -155,7 +160,7 @@ def linear(x, w, out_dtype=None):
 
 
 def qk_norm_rope_append(qkv, num_heads, num_kv_heads, head_dim, q_gain, k_gain, eps, rope_table, rotary_dim, k_pool,
-                        v_pool, page_table, tok_seq, tok_pos, seq_slot, write_kv=True):
+                        v_pool, page_table, tok_seq, tok_pos, seq_slot, write_kv=True, pairs=False):
     T = qkv.shape[0]
     H, KV, Dh = num_heads, num_kv_heads, head_dim
     x = qkv.float().view(T, H + 2 * KV, Dh)
@@ -172,6 +177,10 @@ def qk_norm_rope_append(qkv, num_heads, num_kv_heads, head_dim, q_gain, k_gain, 
         half = rotary_dim // 2
         cs = rope_table[tok_pos.long()]            # [T, half, 2]
         c, s = cs[:, None, :, 0], cs[:, None, :, 1]
+        if pairs:
+            a, b2 = t[..., 0:rotary_dim:2], t[..., 1:rotary_dim:2]
+            turned = torch.stack([a * c - b2 * s, b2 * c + a * s], dim=-1).flatten(-2)
+            return torch.cat([turned, t[..., rotary_dim:]], dim=-1)
         lo, hi, rest = t[..., :half], t[..., half:rotary_dim], t[..., rotary_dim:]
         return torch.cat([lo * c - hi * s, hi * c + lo * s, rest], dim=-1)
 
@@ -187,7 +196,7 @@ def qk_norm_rope_append(qkv, num_heads, num_kv_heads, head_dim, q_gain, k_gain, 
     return q.to(qkv.dtype).contiguous()
 
 
-def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_new, scale, window=0, sink=None):
+def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_new, scale, window=0, sink=None, chunk=0):
     T, H, Dh = q.shape
     KV, P = k_pool.shape[1], k_pool.shape[2]
     G = H // KV
@@ -197,7 +206,7 @@ def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_n
         slot = int(seq_slot[b])
         for t in range(t0, t1):
             pos = n - (t1 - t0) + (t - t0)
-            first = max(0, pos - window + 1) if window > 0 else 0
+            first = max(0, pos - window + 1) if window > 0 else (pos - pos % chunk if chunk > 0 else 0)
             idx = torch.arange(first, pos + 1)
             pages = page_table[slot, (idx // P).long()].long()
             assert (pages >= 0).all(), "read from an unmapped page"
@@ -243,3 +252,130 @@ def sample(logits, temperature, uniform, top_k=None, top_p=None, penalty=None, s
 
 def mark_seen(seen, rows, tokens):
     seen[rows.long(), tokens.long()] = 1
+
+
+# ---- the parts of the third architecture ------------------------------------------------------------------------------
+def scale_(x, factor):
+    x *= factor
+    return x
+
+
+def embed_pair_hash(ids, table, pairs, last_token, tok_seq, tok_pos, seq_slot, seq_start, mul_prev, mul_cur, single=False):
+    T = ids.numel()
+    buckets = pairs.shape[0] - 1
+    out = torch.zeros(T, table.shape[1])
+    for t in range(T):
+        b = int(tok_seq[t])
+        row = buckets
+        if int(tok_pos[t]) > 0:
+            prev = int(ids[t - 1]) if t > int(seq_start[b]) else int(last_token[int(seq_slot[b])])
+            row = (prev * mul_prev + int(ids[t]) * mul_cur) % buckets
+        out[t] = table[int(ids[t])].float() + pairs[row].float()
+    for b in range(seq_slot.numel()):
+        if int(seq_start[b + 1]) > int(seq_start[b]):
+            last_token[int(seq_slot[b])] = ids[int(seq_start[b + 1]) - 1]
+    return out
+
+
+def short_conv(x, col0, weight, state, tok_seq, seq_slot, seq_start, single=False):
+    C, taps = weight.shape
+    xin = x[:, col0:col0 + C].float()
+    y = torch.zeros(x.shape[0], C)
+    for b in range(seq_slot.numel()):
+        t0, t1 = int(seq_start[b]), int(seq_start[b + 1])
+        hist = torch.cat([state[int(seq_slot[b])], xin[t0:t1]], dim=0)          # [taps-1 + n, C]
+        for i in range(t1 - t0):
+            y[t0 + i] = (hist[i:i + taps] * weight.t()).sum(0)
+        if taps > 1:
+            state[int(seq_slot[b])] = hist[hist.shape[0] - (taps - 1):]
+    return y / (1.0 + torch.exp(-y))
+
+
+def delta_rule_recurrent(qkv, q_col, k_col, v_col, proj, beta_col, z, dt_bias, a_log, qscale, state, seq_slot, seq_start,
+                         heads, qk_heads, dim, vdim, single=False):
+    T = qkv.shape[0]
+    rep = heads // qk_heads
+    q = qkv[:, q_col:q_col + qk_heads * dim].view(T, qk_heads, dim)
+    k = qkv[:, k_col:k_col + qk_heads * dim].view(T, qk_heads, dim)
+    q = (q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * qscale).repeat_interleave(rep, dim=1)
+    k = (k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)).repeat_interleave(rep, dim=1)
+    v = qkv[:, v_col:v_col + heads * vdim].view(T, heads, vdim)
+    beta = torch.sigmoid(proj[:, beta_col:beta_col + heads].float())
+    g = torch.exp(-torch.exp(a_log)[None, :, None] * torch.nn.functional.softplus((z.float() + dt_bias).view(T, heads, dim)))
+    o = torch.zeros(T, heads, vdim)
+    for b in range(seq_slot.numel()):
+        S = state[int(seq_slot[b])]
+        for t in range(int(seq_start[b]), int(seq_start[b + 1])):
+            S.mul_(g[t][:, :, None])
+            u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, k[t]))
+            S.add_(k[t][:, :, None] * u[:, None, :])
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    return o
+
+
+def gated_act(gate_up, kind, block=None, limit=0.0, alpha=1.0):
+    rows, two = gate_up.shape
+    inter = two // 2
+    block = block or inter
+    v = gate_up.float().view(rows, inter // block, 2, block)
+    g, u = v[:, :, 0, :].reshape(rows, inter), v[:, :, 1, :].reshape(rows, inter)
+    if kind == "silu":
+        r = g * torch.sigmoid(g) * u
+    elif kind == "gelu_tanh":
+        r = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3))) * u
+    else:
+        g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+        r = g * torch.sigmoid(alpha * g) * (u + 1.0)
+    return r.to(gate_up.dtype)
+
+
+def linear_gated(x, w_gate_up, block, kind="silu", limit=0.0, alpha=1.0):
+    return gated_act(linear(x, w_gate_up), kind, block, limit, alpha)
+
+
+def moe_route(x, router, correction, top):
+    s = torch.softmax(x.float() @ router.t(), dim=-1)
+    c = s + correction
+    idx = torch.zeros(x.shape[0], top, dtype=torch.int32)
+    for j in range(top):
+        at = torch.argmax(c, dim=-1)                    # the first of equals
+        idx[:, j] = at.to(torch.int32)
+        c[torch.arange(x.shape[0]), at] = -math.inf
+    w = torch.gather(s, 1, idx.long())
+    return idx, w / (w.sum(-1, keepdim=True) + 1e-20)
+
+
+def moe_plan(idx, experts):
+    flat = idx.flatten()
+    perm = torch.tensor([p for e in range(experts) for p in torch.nonzero(flat == e).flatten().tolist()], dtype=torch.int32)
+    tiles = torch.tensor([[e, 0, 0] for e in range(experts)], dtype=torch.int32)
+    off = 0
+    for e in range(experts):
+        n = int((flat == e).sum())
+        tiles[e, 1], tiles[e, 2] = off, n
+        off += n
+    return perm, tiles, torch.tensor([experts, off], dtype=torch.int32)
+
+
+def moe_grouped_linear(a, w, plan, rows_out, gather_div=0, scatter=False, out_dtype=None):
+    perm, tiles, meta = plan
+    y = torch.zeros(rows_out, w.shape[1], dtype=out_dtype or a.dtype)
+    for e, r0, n in tiles[:int(meta[0])].tolist():
+        for r in range(r0, r0 + n):
+            src = int(perm[r]) // gather_div if gather_div > 0 else r
+            dst = int(perm[r]) if scatter else r
+            y[dst] = (w[e].double() @ a[src].double()).to(y.dtype)
+    return y
+
+
+def moe_combine(pair_out, idx, weight, x, experts, extra=None):
+    T, D = x.shape
+    top = idx.shape[1]
+    y = torch.zeros(T, D)
+    for j in range(top):
+        ident = (idx[:, j] >= experts)[:, None]
+        v = torch.where(ident, x.float(), pair_out.view(T, top, D)[:, j])
+        y += weight[:, j:j + 1] * v
+    if extra is not None:
+        y += extra.float()
+    return y.to(x.dtype)
