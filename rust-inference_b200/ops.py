@@ -559,6 +559,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     N, K2 = w.shape
     if K != K2:
         raise KernelError(f"linear: x has {K} columns, w has {K2}")
+    if x.data_ptr() % 16:
+        x = x.clone()            # a one-row slice of a wider matrix: the kernels read 16-byte pieces
     if x.dtype == torch.float32:
         y = torch.empty((M, N), dtype=torch.float32, device=x.device)
         _call("linear_f32", "ri_linear_f32", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, _stream())

@@ -51,14 +51,26 @@ class GatedDeltaRule(Mixer):
     def load(self, tensors):
         s = self.spec
         qk, vw = s.num_qk_heads * s.dim, s.num_heads * s.vdim
-        self.proj = torch.cat([tensors[n] for n in ("q", "k", "v", "b", "a1", "g1")], dim=0).contiguous()
+
+        def rows8(t):            # zero rows up to a multiple of 8: every block of columns of the product starts on 16 bytes
+            pad = -t.shape[0] % 8
+            return t if not pad else torch.cat([t, t.new_zeros((pad, t.shape[1]))], dim=0)
+
+        def cols8(t):            # ... and the matrices that read the padded blocks get zero columns
+            pad = -t.shape[1] % 8
+            return t if not pad else torch.cat([t, t.new_zeros((t.shape[0], pad))], dim=1)
+
+        blocks = [rows8(torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0)), rows8(tensors["b"]),
+                  rows8(tensors["a1"]), rows8(tensors["g1"])]
+        self.proj = torch.cat(blocks, dim=0).contiguous()
         self.channels = 2 * qk + vw
         self.q_col, self.k_col, self.v_col = 0, qk, 2 * qk
-        self.b_col = self.channels
-        self.a_col = self.b_col + s.num_heads
-        self.g_col = self.a_col + s.decay_rank
+        self.b_col = blocks[0].shape[0]
+        self.a_col = self.b_col + blocks[1].shape[0]
+        self.g_col = self.a_col + blocks[2].shape[0]
+        self.a_rank, self.g_rank = blocks[2].shape[0], blocks[3].shape[0]
         self.conv = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).contiguous()
-        self.a2, self.g2 = tensors["a2"].contiguous(), tensors["g2"].contiguous()
+        self.a2, self.g2 = cols8(tensors["a2"]).contiguous(), cols8(tensors["g2"]).contiguous()
         self.dt_bias, self.a_log, self.gain = tensors["dt_bias"], tensors["A_log"], tensors["norm"]
         self.o = tensors["o"].contiguous()
 
@@ -81,8 +93,8 @@ class GatedDeltaRule(Mixer):
         with section("delta q/k/v/beta/low-rank proj"):
             proj = ops.linear(x, self.proj)
         with section("delta decay and gate proj"):
-            za = ops.linear(proj[:, self.a_col:self.a_col + s.decay_rank].contiguous(), self.a2)
-            zg = ops.linear(proj[:, self.g_col:self.g_col + s.gate_rank].contiguous(), self.g2)
+            za = ops.linear(proj[:, self.a_col:self.a_col + self.a_rank].contiguous(), self.a2)
+            zg = ops.linear(proj[:, self.g_col:self.g_col + self.g_rank].contiguous(), self.g2)
         with section("delta conv"):
             qkv = ops.short_conv(proj, 0, self.conv, cache.more_state[0], ctx.tok_seq, ctx.seq_slot, ctx.seq_start, single=single)
         with section("delta recurrence"):
