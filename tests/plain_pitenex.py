@@ -72,7 +72,7 @@ def rotate_pairs(x, dims, base):
 
 
 def chunked_attention(h, w, m):
-    """h [n, width]; w: the tensors q, k, v, sink, o; m: heads, kv_heads, dim, vdim, rot, scale, mask.size."""
+    """h [n, width]; w: the tensors q, k, v, sink, o; m: heads, kv_heads, dim, vdim, rot, scale, mask.size (absent: none)."""
     n = h.shape[0]
     H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (h @ w["q"].T).reshape(n, H, dim)
@@ -81,7 +81,7 @@ def chunked_attention(h, w, m):
     rot = m.get("rot")
     if rot and rot["dims"]:
         q, k = rotate_pairs(q, rot["dims"], float(rot["base"])), rotate_pairs(k, rot["dims"], float(rot["base"]))
-    size = m["mask"]["size"]
+    size = (m.get("mask") or {}).get("size") or n + 1          # no mask: every earlier key
     out = np.zeros((n, H, vdim), dtype=F64)
     for p in range(n):
         lo = (p // size) * size
