@@ -18,10 +18,11 @@ steps end at exactly 4,096 tokens.  One JSON line is printed:
   points     decode tokens a second at batch 1 and 64 (device-timed), and the same through
              the Python entry point (e2e_b1, e2e_b64)
 
-    python bench.py --design ranudra [--size small|large]
+    python bench.py --design ranudra|pitenex [--size small|large]
 
-measures the Ranudra design (latent attention, gated linear attention, hyper-connections) at layer sizes that
-resemble a real model's, beside a Qwen3 model of the same width, depth and parameter count: decode at batch 8 and a
+measures another design (Ranudra: latent attention, gated linear attention, hyper-connections; Pitenex: chunked attention
+with a sink beside the gated delta rule, dense and routed feed-forwards) at layer sizes that
+resemble a real model's, beside a Qwen3 model of the same width and depth: decode at batch 8 and a
 prompt step of 2,048 tokens, device-timed, and the device time of every section of both steps from eager runs with
 the section timers on, with the bytes or flops of the sections that have a roofline.  One JSON line.
 
@@ -278,6 +279,30 @@ def ranudra_config(z) -> dict:
             "streams": 4, "layers": [gla, la, la2] * (z["layers"] // 3)}
 
 
+def pitenex_config(z) -> dict:
+    """Layers that alternate a gelu-gated dense feed-forward and a routed one (16 experts and 2 identity experts, 4 per
+    token, a shared expert), each beside a mixer of chunked attention with a sink (keys and values of 128, four query
+    heads per key/value head, chunks of 2,048 positions) and the gated delta rule (heads of 128 x 128, half as many as
+    the attention has, a convolution of 4 taps, low-rank projections of 64)."""
+    D, H = z["width"], z["heads"]
+    left = {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "rot": {"base": 500000.0, "dims": 64}, "mask": {"size": 2048}}
+    right = {"heads": max(1, H // 2), "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64,
+             "gate_rank": 64}
+    mixer = {"left": left, "right": right, "left_scale": 0.8, "right_scale": 1.1}
+    inter = -(-(2 * z["ff"] // 3) // 256) * 256          # three matrices of a gated feed-forward against two
+    dense = {"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": inter}}
+    moe = {"type": "parallel", "mixer": mixer,
+           "mlp": {"kind": "moe", "router": {"experts": 16, "identity": 2, "top": 4},
+                   "expert": {"ff": inter // 8, "limit": 7.0}, "shared": {"ff": inter // 4, "limit": 7.0}}}
+    return {"architecture": "Pitenex", "vocab": z["vocab"], "width": D,
+            "embedding": {"bigram": {"buckets": 8191, "mul_prev": 127, "mul_cur": 7}}, "norm": {"eps": 1e-6},
+            "residual_mult": 0.7, "logit_scale": 1.0, "layers": [dense, moe] * (z["layers"] // 2)}
+
+
+DESIGNS = {"ranudra": ranudra_config, "pitenex": pitenex_config}
+
+
 def qwen3_like(z) -> dict:
     inter = -(-(2 * z["ff"] // 3) // 256) * 256          # three matrices of SwiGLU against two: the same parameters
     return dict(QWEN3_8B, num_hidden_layers=z["layers"], hidden_size=z["width"], num_attention_heads=z["heads"],
@@ -302,7 +327,7 @@ def run_design(a) -> int:
     clocks.start()
     windows = []
     out = {}
-    for label, cfg in (("ranudra", ranudra_config(z)), ("qwen3", qwen3_like(z))):
+    for label, cfg in ((a.design, DESIGNS[a.design](z)), ("qwen3", qwen3_like(z))):
         t_model = time.time()
         model = Model.from_random(cfg, seed=1, dtype="bfloat16", device=dev)
         V = model.spec.vocab_size
@@ -381,16 +406,16 @@ def run_design(a) -> int:
         del engine, model
         torch.cuda.empty_cache()
     clocks.stop()
-    r = out["ranudra"]
+    r = out[a.design]
     line = {
-        "metric": f"decode tok/s at batch {B}, context {ctx} (Ranudra, {a.size} layer shapes, bf16)",
+        "metric": f"decode tok/s at batch {B}, context {ctx} ({a.design.capitalize()}, {a.size} layer shapes, bf16)",
         "value": r["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm,
         "ms_per_step": r["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: random-init weights, uniform random token ids", "design": "ranudra",
+        "dtype": "bf16", "data": "synthetic: random-init weights, uniform random token ids", "design": a.design,
         "config": dict(z, size=a.size, global_batch=B, seq_len=ctx, prefill_tokens=T, parallelism="1 GPU", peaks=peak_src,
-                       beside="a Qwen3 model of the same width, depth and parameter count"),
+                       beside="a Qwen3 model of the same width and depth (weight_bytes of both are given)"),
         "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops},
-        "ranudra": r, "qwen3": out["qwen3"], "clocks": clocks.summary(windows), "gpu_launches": r["decode_launches"] * K,
+        a.design: r, "qwen3": out["qwen3"], "clocks": clocks.summary(windows), "gpu_launches": r["decode_launches"] * K,
         "impl": "ours",
     }
     print(json.dumps(line))
@@ -416,7 +441,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS),
                     help="run a whole workload of the larger sizes through LLM.generate instead of the default line")
-    ap.add_argument("--design", choices=["ranudra"],
+    ap.add_argument("--design", choices=sorted(DESIGNS),
                     help="measure another design beside a Qwen3 model of equal size instead of the default line")
     ap.add_argument("--size", default="small", choices=sorted(DESIGN_SIZES), help="layer sizes of --design")
     a = ap.parse_args()

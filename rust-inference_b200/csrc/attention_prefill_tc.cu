@@ -285,6 +285,7 @@ struct TcWork {
     const int* seq_start;
     const int* seq_len;
     int seqs, H, KV, mpps, groups_max, n_items, window;
+    const float* sink;          // [H] or null: exp(sink[h]) joins head h's softmax denominator, with no key and no value
 };
 // The items in the order (group of rows: late ones, which see the most keys, first; sequence; head).  Block c of G
 // takes item k G + c in its round k when k is even and item k G + G - 1 - c when k is odd, so the block that drew
@@ -308,7 +309,7 @@ __device__ __forceinline__ bool tc_item(const TcWork& w, int k, TcItem& it) {
     it.n_tiles = it.rows > TC_BM ? 2 : 1;
     it.pos_first = it.len - n_new + r_base;
     it.pos_last = it.pos_first + it.rows - 1;
-    it.key_lo = (w.window > 0 && it.pos_first - w.window + 1 > 0) ? it.pos_first - w.window + 1 : 0;
+    it.key_lo = ri_first_visible(it.pos_first, w.window);
     it.kb_lo = it.key_lo / TC_BN;
     it.n_blocks = it.pos_last / TC_BN - it.kb_lo + 1;
     it.n_blocks_0 = it.n_tiles > 1 ? min(it.n_blocks, (it.pos_first + TC_BM - 1) / TC_BN - it.kb_lo + 1) : it.n_blocks;
@@ -569,12 +570,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 __syncwarp();
                 if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.s_read[t][idx & 1])) : "memory");
                 // a block of keys needs the mask if some query of this tile does not see all of it
-                const bool edge = (kb * TC_BN + TC_BN - 1 > tile_first) || (window > 0 && kb * TC_BN < tile_last - window + 1);
+                const bool edge = (kb * TC_BN + TC_BN - 1 > tile_first) || (window != 0 && kb * TC_BN < ri_first_visible(tile_last, window));
                 if (edge) {
+                    const int first_vis = ri_first_visible(my_pos, window);
 #pragma unroll
                     for (int i = 0; i < TC_BN; i++) {
                         int key = kb * TC_BN + i;
-                        bool vis = key <= my_pos && (window <= 0 || key > my_pos - window);
+                        bool vis = key <= my_pos && key >= first_vis;
                         s[i] = vis ? s[i] : -FLT_MAX;
                     }
                 }
@@ -678,6 +680,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!dead && !tc_mbar_wait(&tail.pv_done[t][last & 1], (unsigned)((last >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
             tc_fence_after();
             const bool mine = real_row && !dead;
+            // (m is the running maximum in units of log2, possibly a little below the true one: l and O are both relative to it)
+            if (work.sink && m != -FLT_MAX) l += ex2_approx(work.sink[it.h] * 1.4426950408889634f - m);
             const float inv = 1.0f / l;
             bf16* dst = out + ((size_t)(it.t_first + (mine ? t * TC_BM + row : 0)) * H + it.h) * TC_DH;
 #pragma unroll
@@ -775,14 +779,13 @@ extern "C" int ri_attention_prefill_tc_head_dim() { return TC_DH; }
 extern "C" int ri_attention_prefill_tc(const void* q, const void* k_pool, const void* v_pool, void* out,
                                        const int* page_table, const int* seq_slot, const int* seq_start,
                                        const int* seq_len, int tokens, int seqs, int max_new, int H, int KV, int Dh, int mpps,
-                                       int page_size, int num_pages, float scale, int window, int* err_flag,
-                                       cudaStream_t stream) {
+                                       int page_size, int num_pages, float scale, int window, const float* sink,
+                                       int* err_flag, cudaStream_t stream) {
     if (seqs == 0 || max_new == 0 || tokens == 0) return 0;
     RI_REQUIRE(Dh == TC_DH, "attention_prefill_tc: built for head_dim %d, called with %d", TC_DH, Dh);
     RI_REQUIRE(page_size == TC_PAGE, "attention_prefill_tc: pages of %d tokens, this kernel needs %d", page_size, TC_PAGE);
     RI_REQUIRE(H > 0 && KV > 0 && H % KV == 0, "attention_prefill_tc: %d heads over %d kv heads", H, KV);
     RI_REQUIRE(tokens > 0 && max_new > 0 && max_new <= tokens, "attention_prefill_tc: %d tokens, at most %d of one sequence", tokens, max_new);
-    RI_REQUIRE(window >= 0, "attention_prefill_tc: negative window");
     RI_REQUIRE(scale > 0.0f, "attention_prefill_tc: the score scale must be positive");
     RI_REQUIRE((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) == 0,
                "attention_prefill_tc: q, out and the pools must be 16-byte aligned");
@@ -820,6 +823,7 @@ extern "C" int ri_attention_prefill_tc(const void* q, const void* k_pool, const 
     work.groups_max = groups_max;
     work.n_items = (int)n_items;
     work.window = window;
+    work.sink = sink;
     // one block per SM (the kernel's shared memory allows no second), each taking its items one after the other
     const int blocks = n_items < sms ? (int)n_items : sms;
     attention_prefill_tc_kernel<<<blocks, TC_THREADS, TC_SMEM_BYTES, stream>>>(

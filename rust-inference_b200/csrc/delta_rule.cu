@@ -13,12 +13,13 @@
 //     beta = sigmoid(b[h])
 //     S[d, j] <- g[d] S[d, j];   u[j] = beta (v[j] - sum_d S[d, j] kn[d]);   S[d, j] <- S[d, j] + kn[d] u[j]
 //     o[j] = sum_d S[d, j] qn[d]                                              (reads the current token's write)
+//          = sum_d (g[d] S_old[d, j]) qn[d] + u[j] (kn . qn)                   (the form the kernel computes)
 // all in float32; S [dim, vdim] lives in the sequence's slot of `state` [slots, H, dim, vdim].
-// A block owns 32 value columns of one (sequence, head); a column is shared by four neighbouring lanes, each with a
-// quarter of the key channels in registers (channel d = part + 4 i).  The block stages GROUP tokens at a time in
-// shared memory (normalised q and k, decay, beta, values); the sums over d are taken over each lane's channels in
-// ascending order and then over the four lanes by two shuffles, an order that depends on the head's size only, so the
-// result does not depend on how a sequence's tokens were cut into steps.
+// What does not depend on the token before (unit vectors, decays, beta) is computed for all tokens at once by a kernel
+// of its own; the recurrence kernel only walks the tokens.  There a block owns 32 value columns of one (sequence, head);
+// a column is shared by four neighbouring lanes, each with a quarter of the key channels in registers.  Every sum over
+// d has one order that depends on the head's size only, so the result does not depend on how a sequence's tokens were
+// cut into steps.
 #include "common.cuh"
 
 __device__ __forceinline__ float dr_silu(float z) { return z / (1.0f + expf(-z)); }
@@ -97,131 +98,219 @@ extern "C" int ri_short_conv(const void* x, long long ld, int col0, const float*
     return 0;
 }
 
-// ---- the recurrence -------------------------------------------------------------------------------------------------
-#define DR_SPLIT 4                  // lanes that share a value column
-#define DR_BCOLS 32                 // value columns per block
-#define DR_THREADS (DR_SPLIT * DR_BCOLS)
+// ---- what the recurrence reads, made ready for all tokens at once ------------------------------------------------------
+// One block per token: q and k of every q/k head become unit vectors in place (q also times qscale), the decays
+// g[h, d] = exp(-exp(A_log[h]) softplus(z[h, d] + dt_bias[h, d])), beta[h] = sigmoid(b[h]) and the products k . q of the
+// unit vectors are written as float32 (`beta` [tokens, H + G]: the betas, then the products).
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prep_kernel(float* __restrict__ qkv, int C, int q_col, int k_col, const T* __restrict__ proj, long long ld, int b_col,
+                  const T* __restrict__ z, const float* __restrict__ dt_bias, const float* __restrict__ a_log, float qscale,
+                  float* __restrict__ decay, float* __restrict__ beta, int H, int G, int dim) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* row = qkv + (size_t)t * C;
+    for (int g = warp; g < G; g += 4) {                        // a warp per q/k head: both unit vectors and their product
+        float* q = row + q_col + g * dim;
+        float* k = row + k_col + g * dim;
+        float sq = 0.0f, sk = 0.0f, qk = 0.0f;
+        for (int d = lane; d < dim; d += 32) {
+            sq = fmaf(q[d], q[d], sq);
+            sk = fmaf(k[d], k[d], sk);
+            qk = fmaf(q[d], k[d], qk);
+        }
+        const float iq = qscale / sqrtf(warp_sum(sq) + 1e-6f), ik = 1.0f / sqrtf(warp_sum(sk) + 1e-6f);
+        qk = warp_sum(qk);
+        for (int d = lane; d < dim; d += 32) {
+            q[d] *= iq;
+            k[d] *= ik;
+        }
+        if (lane == 0) beta[(size_t)t * (H + G) + H + g] = qk * iq * ik;
+    }
+    for (int i = threadIdx.x; i < H * dim; i += blockDim.x) {
+        const float rate = expf(a_log[i / dim]);
+        decay[(size_t)t * H * dim + i] = expf(-rate * dr_softplus(ld_f(z + (size_t)t * H * dim + i) + dt_bias[i]));
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+        beta[(size_t)t * (H + G) + h] = 1.0f / (1.0f + expf(-ld_f(proj + (size_t)t * ld + b_col + h)));
+}
 
-// CH: key channels per lane (dim <= 4 CH); GROUP: tokens staged at a time
-template <typename T, int CH, int GROUP>
+// ---- the recurrence -------------------------------------------------------------------------------------------------
+#define DR_THREADS 64
+
+// SPLIT: neighbouring lanes that share a value column (a block owns DR_THREADS / SPLIT columns); CH: key channels per
+// lane (dim <= SPLIT CH; lane `part` of a column has channels 4 SPLIT i + 4 part .. + 3, so that the lanes of a column
+// read neighbouring 16-byte pieces of a staged vector); GROUP: tokens staged at a time.  The recurrence is a chain from
+// token to token, so a warp's time per token is what counts: many lanes per column keep the chain short (a handful of
+// channels per lane, then log2(SPLIT) shuffles), and the many small blocks put warps on every SM even for one sequence.
+// The next group's values are loaded into registers before the group at hand is computed and stored into the other of
+// two buffers afterwards: one barrier per group, and memory works while the arithmetic runs.  A sum over d is taken in
+// four partial sums per lane (channels 4 i + j into sum j), added as (s0 + s1) + (s2 + s3), then over the lanes.
+// The read-out after the write, o = (S' + k u^T)^T q with S' the decayed state, is taken as S'^T q + u (k . q): both
+// sums over d then run over the same S' side by side (their shuffles travel together), and the write S' + k u^T is
+// off the chain to the next token's sums by one multiply-add.
+template <int CH, int SPLIT, int GROUP>
 __global__ void __launch_bounds__(DR_THREADS)
-delta_rule_kernel(const float* __restrict__ qkv, int C, int q_col, int k_col, int v_col, const T* __restrict__ proj,
-                  long long ld, int b_col, const T* __restrict__ z, const float* __restrict__ dt_bias,
-                  const float* __restrict__ a_log, float qscale, float* __restrict__ state, float* __restrict__ o,
+delta_rule_kernel(const float* __restrict__ qkv, int C, int q_col, int k_col, int v_col, const float* __restrict__ decay,
+                  const float* __restrict__ beta, float* __restrict__ state, float* __restrict__ o,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int H, int G, int dim, int vdim) {
-    constexpr int DIMC = CH * DR_SPLIT;
-    __shared__ float s_g[GROUP][DIMC], s_k[GROUP][DIMC], s_q[GROUP][DIMC], s_v[GROUP][DR_BCOLS], s_beta[GROUP];
+    constexpr int DIMC = CH * SPLIT;
+    constexpr int DR_BCOLS = DR_THREADS / SPLIT;
+    constexpr int PER = (GROUP * DIMC + DR_THREADS - 1) / DR_THREADS;      // staged elements per thread and array
+    constexpr int VPER = (GROUP * DR_BCOLS + DR_THREADS - 1) / DR_THREADS;
+    __shared__ __align__(16) float s_g[2][GROUP][DIMC], s_k[2][GROUP][DIMC], s_q[2][GROUP][DIMC];
+    __shared__ float s_v[2][GROUP][DR_BCOLS], s_beta[2][GROUP], s_kq[2][GROUP];
+    static_assert(2 * GROUP <= DR_THREADS, "a thread per staged beta and per staged product");
     pdl_trigger();
     const int b = blockIdx.z, h = blockIdx.y;
     const int kvh = h / (H / G);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int part = threadIdx.x % DR_SPLIT, col = threadIdx.x / DR_SPLIT;
+    const int part = threadIdx.x % SPLIT, col = threadIdx.x / SPLIT;
     const int j = blockIdx.x * DR_BCOLS + col;
     const bool mine = j < vdim;
-    const float rate = expf(a_log[h]);
     pdl_wait();
     const int t0 = seq_start[b], t1 = seq_start[b + 1];
     float* st = state + ((size_t)seq_slot[b] * H + h) * dim * vdim;
     float S[CH];
 #pragma unroll
     for (int i = 0; i < CH; i++) {
-        const int d = part + DR_SPLIT * i;
+        const int d = 4 * SPLIT * (i / 4) + 4 * part + (i & 3);
         S[i] = (mine && d < dim) ? st[(size_t)d * vdim + j] : 0.0f;
     }
+    float rg[PER], rk[PER], rq[PER], rv[VPER], rb = 0.0f;
+    auto fetch = [&](int base) {
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const int idx = threadIdx.x + e * DR_THREADS;
+            const int g = idx / DIMC, d = idx % DIMC, t = base + g;
+            rg[e] = rk[e] = rq[e] = 0.0f;
+            if (g < GROUP && t < t1 && d < dim) {
+                rg[e] = decay[((size_t)t * H + h) * dim + d];
+                rk[e] = qkv[(size_t)t * C + k_col + kvh * dim + d];
+                rq[e] = qkv[(size_t)t * C + q_col + kvh * dim + d];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VPER; e++) {
+            const int idx = threadIdx.x + e * DR_THREADS;
+            const int g = idx / DR_BCOLS, jj = blockIdx.x * DR_BCOLS + idx % DR_BCOLS;
+            rv[e] = (g < GROUP && base + g < t1 && jj < vdim) ? qkv[(size_t)(base + g) * C + v_col + h * vdim + jj] : 0.0f;
+        }
+        if (threadIdx.x < 2 * GROUP) {
+            const int g = threadIdx.x % GROUP;
+            rb = base + g < t1 ? beta[(size_t)(base + g) * (H + G) + (threadIdx.x < GROUP ? h : H + kvh)] : 0.0f;
+        }
+    };
+    auto store = [&](int buf) {
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const int idx = threadIdx.x + e * DR_THREADS;
+            if (idx < GROUP * DIMC) {
+                (&s_g[buf][0][0])[idx] = rg[e];
+                (&s_k[buf][0][0])[idx] = rk[e];
+                (&s_q[buf][0][0])[idx] = rq[e];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VPER; e++) {
+            const int idx = threadIdx.x + e * DR_THREADS;
+            if (idx < GROUP * DR_BCOLS) (&s_v[buf][0][0])[idx] = rv[e];
+        }
+        if (threadIdx.x < GROUP) s_beta[buf][threadIdx.x] = rb;
+        else if (threadIdx.x < 2 * GROUP) s_kq[buf][threadIdx.x - GROUP] = rb;
+    };
+    fetch(t0);
+    int buf = 0;
     for (int base = t0; base < t1; base += GROUP) {
-        __syncthreads();                                         // the group before has been used
-        // a warp stages a token: unit vectors of q and k, the decays, beta
-        for (int g = warp; g < GROUP; g += DR_THREADS / 32) {
-            const int t = base + g;
-            if (t >= t1) break;
-            const float* row = qkv + (size_t)t * C;
-            float sq = 0.0f, sk = 0.0f;
-            for (int d = lane; d < dim; d += 32) {
-                const float qv = row[q_col + kvh * dim + d], kv = row[k_col + kvh * dim + d];
-                sq = fmaf(qv, qv, sq);
-                sk = fmaf(kv, kv, sk);
-            }
-            const float iq = qscale / sqrtf(warp_sum(sq) + 1e-6f), ik = 1.0f / sqrtf(warp_sum(sk) + 1e-6f);
-            for (int d = lane; d < DIMC; d += 32) {
-                const bool in = d < dim;
-                s_q[g][d] = in ? row[q_col + kvh * dim + d] * iq : 0.0f;
-                s_k[g][d] = in ? row[k_col + kvh * dim + d] * ik : 0.0f;
-                s_g[g][d] = in ? expf(-rate * dr_softplus(ld_f(z + ((size_t)t * H + h) * dim + d) + dt_bias[h * dim + d])) : 0.0f;
-            }
-            if (lane == 0) s_beta[g] = 1.0f / (1.0f + expf(-ld_f(proj + (size_t)t * ld + b_col + h)));
-        }
-        for (int i = threadIdx.x; i < GROUP * DR_BCOLS; i += DR_THREADS) {
-            const int g = i / DR_BCOLS, cc = i % DR_BCOLS, jj = blockIdx.x * DR_BCOLS + cc;
-            s_v[g][cc] = (base + g < t1 && jj < vdim) ? qkv[(size_t)(base + g) * C + v_col + h * vdim + jj] : 0.0f;
-        }
-        __syncthreads();
+        store(buf);
+        __syncthreads();             // this group is staged (the other buffer was last read before the barrier before)
+        if (base + GROUP < t1) fetch(base + GROUP);
         const int n = min(GROUP, t1 - base);
         for (int g = 0; g < n; g++) {
-            float pred = 0.0f;
+            float p[4] = {0.0f, 0.0f, 0.0f, 0.0f}, a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float4 kr[CH / 4];
 #pragma unroll
-            for (int i = 0; i < CH; i++) {
-                const int d = part + DR_SPLIT * i;
-                S[i] *= s_g[g][d];
-                pred = fmaf(S[i], s_k[g][d], pred);
+            for (int i = 0; i < CH; i += 4) {
+                const int at = 4 * SPLIT * (i / 4) + 4 * part;
+                const float4 gg = *reinterpret_cast<const float4*>(&s_g[buf][g][at]);
+                const float4 kk = *reinterpret_cast<const float4*>(&s_k[buf][g][at]);
+                const float4 qq = *reinterpret_cast<const float4*>(&s_q[buf][g][at]);
+                kr[i / 4] = kk;
+                S[i] *= gg.x;     p[0] = fmaf(S[i], kk.x, p[0]);     a[0] = fmaf(S[i], qq.x, a[0]);
+                S[i + 1] *= gg.y; p[1] = fmaf(S[i + 1], kk.y, p[1]); a[1] = fmaf(S[i + 1], qq.y, a[1]);
+                S[i + 2] *= gg.z; p[2] = fmaf(S[i + 2], kk.z, p[2]); a[2] = fmaf(S[i + 2], qq.z, a[2]);
+                S[i + 3] *= gg.w; p[3] = fmaf(S[i + 3], kk.w, p[3]); a[3] = fmaf(S[i + 3], qq.w, a[3]);
             }
-            pred += __shfl_xor_sync(0xffffffffu, pred, 1);
-            pred += __shfl_xor_sync(0xffffffffu, pred, 2);
-            const float u = s_beta[g] * (s_v[g][col] - pred);
-            float acc = 0.0f;
+            float pred = (p[0] + p[1]) + (p[2] + p[3]);
+            float acc = (a[0] + a[1]) + (a[2] + a[3]);
 #pragma unroll
-            for (int i = 0; i < CH; i++) {
-                const int d = part + DR_SPLIT * i;
-                S[i] = fmaf(s_k[g][d], u, S[i]);
-                acc = fmaf(S[i], s_q[g][d], acc);
+            for (int sh = 1; sh < SPLIT; sh <<= 1) {
+                pred += __shfl_xor_sync(0xffffffffu, pred, sh);
+                acc += __shfl_xor_sync(0xffffffffu, acc, sh);
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            const float u = s_beta[buf][g] * (s_v[buf][g][col] - pred);
+#pragma unroll
+            for (int i = 0; i < CH; i += 4) {
+                S[i] = fmaf(kr[i / 4].x, u, S[i]);
+                S[i + 1] = fmaf(kr[i / 4].y, u, S[i + 1]);
+                S[i + 2] = fmaf(kr[i / 4].z, u, S[i + 2]);
+                S[i + 3] = fmaf(kr[i / 4].w, u, S[i + 3]);
+            }
+            acc = fmaf(u, s_kq[buf][g], acc);
             if (part == 0 && mine) o[((size_t)(base + g) * H + h) * vdim + j] = acc;
         }
+        buf ^= 1;
     }
     if (mine) {
 #pragma unroll
         for (int i = 0; i < CH; i++) {
-            const int d = part + DR_SPLIT * i;
+            const int d = 4 * SPLIT * (i / 4) + 4 * part + (i & 3);
             if (d < dim) st[(size_t)d * vdim + j] = S[i];
         }
     }
 }
 
-// qkv [tokens, C] float32 (the convolution's output): q of q/k head g at columns q_col + g dim .., k at k_col + g dim ..,
-// v of head h at v_col + h vdim ..;  proj [tokens, ld] (compute type): beta's logit of head h at column b_col + h;
-// z [tokens, H dim] (compute type): the decay's projection, dt_bias [H dim] and a_log [H] float32;
+// qkv [tokens, C] float32 (the convolution's output; its q and k columns are made unit vectors in place): q of q/k head g
+// at columns q_col + g dim .., k at k_col + g dim .., v of head h at v_col + h vdim ..;  proj [tokens, ld] (compute type):
+// beta's logit of head h at column b_col + h;  z [tokens, H dim] (compute type): the decay's projection, dt_bias [H dim]
+// and a_log [H] float32;  decay [tokens, H dim] and beta [tokens, H + G]: float32 scratch that this call fills;
 // state [slots, H, dim, vdim] float32, updated in place;  o [tokens, H, vdim] float32.
-extern "C" int ri_delta_rule_recurrent(const float* qkv, int C, int q_col, int k_col, int v_col, const void* proj,
-                                       long long ld, int b_col, const void* z, const float* dt_bias, const float* a_log,
-                                       float qscale, float* state, float* o, const int* seq_slot, const int* seq_start,
-                                       int seqs, int H, int G, int dim, int vdim, int single, int dtype,
-                                       cudaStream_t stream) {
-    if (seqs == 0) return 0;
-    RI_REQUIRE(seqs > 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0, "delta_rule_recurrent: bad sizes");
+extern "C" int ri_delta_rule_recurrent(float* qkv, int C, int q_col, int k_col, int v_col, const void* proj, long long ld,
+                                       int b_col, const void* z, const float* dt_bias, const float* a_log, float qscale,
+                                       float* decay, float* beta, float* state, float* o, const int* seq_slot,
+                                       const int* seq_start, int tokens, int seqs, int H, int G, int dim, int vdim,
+                                       int single, int dtype, cudaStream_t stream) {
+    if (seqs == 0 || tokens == 0) return 0;
+    RI_REQUIRE(seqs > 0 && tokens > 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0, "delta_rule_recurrent: bad sizes");
     RI_REQUIRE(seqs <= 65535 && H <= 65535, "delta_rule_recurrent: %d sequences, %d heads: too many for one launch", seqs, H);
     RI_REQUIRE(dim <= 256, "delta_rule_recurrent: %d key channels per head (up to 256 are built)", dim);
-    RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "delta_rule_recurrent: unknown dtype %d", dtype);
-    const dim3 grid((vdim + DR_BCOLS - 1) / DR_BCOLS, H, seqs);
-#define DR_GO(T, CH, GROUP)                                                                                              \
-    ri_launch_pdl(delta_rule_kernel<T, CH, GROUP>, grid, dim3(DR_THREADS), 0, stream, qkv, C, q_col, k_col, v_col,        \
-                  (const T*)proj, ld, b_col, (const T*)z, dt_bias, a_log, qscale, state, o, seq_slot, seq_start, H, G,   \
-                  dim, vdim)
-#define DR_BY_GROUP(T, CH)                                                                                               \
+    if (dtype == RI_DTYPE_F32)
+        ri_launch_pdl(delta_prep_kernel<float>, dim3(tokens), dim3(128), 0, stream, qkv, C, q_col, k_col, (const float*)proj, ld,
+                      b_col, (const float*)z, dt_bias, a_log, qscale, decay, beta, H, G, dim);
+    else if (dtype == RI_DTYPE_BF16)
+        ri_launch_pdl(delta_prep_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, qkv, C, q_col, k_col,
+                      (const __nv_bfloat16*)proj, ld, b_col, (const __nv_bfloat16*)z, dt_bias, a_log, qscale, decay, beta, H, G, dim);
+    else RI_FAIL(-1, "delta_rule_recurrent: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("delta_prep");
+#define DR_GO(CH, SPLIT, GROUP)                                                                                          \
     do {                                                                                                                 \
-        if (single) DR_GO(T, CH, 1);                                                                                     \
-        else DR_GO(T, CH, (CH > 32 ? 4 : 8));                                                                            \
+        const int bcols = DR_THREADS / SPLIT;                                                                            \
+        const dim3 grid((vdim + bcols - 1) / bcols, H, seqs);                                                            \
+        ri_launch_pdl(delta_rule_kernel<CH, SPLIT, GROUP>, grid, dim3(DR_THREADS), 0, stream, (const float*)qkv, C,       \
+                      q_col, k_col, v_col, (const float*)decay, (const float*)beta, state, o, seq_slot, seq_start, H, G, \
+                      dim, vdim);                                                                                        \
     } while (0)
-#define DR_BY_DIM(T)                                                                                                     \
+#define DR_BY_GROUP(CH, SPLIT, GROUP)                                                                                    \
     do {                                                                                                                 \
-        if (dim <= 32) DR_BY_GROUP(T, 8);                                                                                \
-        else if (dim <= 64) DR_BY_GROUP(T, 16);                                                                          \
-        else if (dim <= 128) DR_BY_GROUP(T, 32);                                                                         \
-        else DR_BY_GROUP(T, 64);                                                                                         \
+        if (single) DR_GO(CH, SPLIT, 1);                                                                                 \
+        else DR_GO(CH, SPLIT, GROUP);                                                                                    \
     } while (0)
-    if (dtype == RI_DTYPE_F32) DR_BY_DIM(float);
-    else DR_BY_DIM(__nv_bfloat16);
-#undef DR_BY_DIM
+    if (dim <= 16) DR_BY_GROUP(4, 4, 16);
+    else if (dim <= 32) DR_BY_GROUP(4, 8, 16);
+    else if (dim <= 64) DR_BY_GROUP(4, 16, 16);
+    else if (dim <= 128) DR_BY_GROUP(8, 16, 8);
+    else DR_BY_GROUP(16, 16, 4);
 #undef DR_BY_GROUP
 #undef DR_GO
     RI_CHECK_LAUNCH("delta_rule_recurrent");

@@ -2,7 +2,7 @@
 //
 // `moe_route`   per token: logits z = R x (float32), scores s = softmax(z) over all N outputs of the router, choice
 //               scores s + correction, the `top` largest of them (ties: the lower index), and as weights the chosen
-//               outputs' scores s divided by their sum (+ 1e-20).  A warp per token; every sum has a fixed order.
+//               outputs' scores s divided by their sum (+ 1e-20).  Every sum has a fixed order.
 // `moe_plan`    the step's (token, choice) pairs grouped by expert: `perm` lists the pairs of expert 0, then of expert
 //               1 and so on (pairs whose choice is not one of the first E outputs, identity experts, are left out), and
 //               `tiles` cuts every expert's run into tiles of MOE_BM rows: (expert, first row in perm, rows).  One
@@ -20,30 +20,47 @@
 #include "mma_helpers.cuh"
 
 #define MOE_BM 32
+#define MOE_BM_WIDE 64
 #define MOE_BN 64
 #define MOE_ROUTE_WARPS 4
 
+// A block takes MOE_ROUTE_TOK tokens: its warps share the router's outputs among them (warp w takes n = w, w + warps, ..)
+// and compute an output's logit for all the block's tokens at once, so a row of the router is read once per block; then a
+// warp per token does the softmax and the choice.  A token's sums do not depend on the tokens beside it.
+#define MOE_ROUTE_TOK 4
 template <typename T>
 __global__ void __launch_bounds__(32 * MOE_ROUTE_WARPS)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
                  int* __restrict__ idx, float* __restrict__ weight, int tokens, int D, int N, int top) {
-    extern __shared__ float moe_sm[];                 // per warp: scores [N], choice scores [N]
+    extern __shared__ float moe_sm[];                 // per token of the block: scores [N], choice scores [N]
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * MOE_ROUTE_WARPS + warp;
-    if (t >= tokens) return;
+    const int tb = blockIdx.x * MOE_ROUTE_TOK;
+    const int nt = min(MOE_ROUTE_TOK, tokens - tb);
+    for (int n = warp; n < N; n += MOE_ROUTE_WARPS) {
+        const float* w = router + (size_t)n * D;
+        float acc[MOE_ROUTE_TOK];
+#pragma unroll
+        for (int i = 0; i < MOE_ROUTE_TOK; i++) acc[i] = 0.0f;
+#pragma unroll 4
+        for (int k = lane; k < D; k += 32) {
+            const float wk = w[k];
+#pragma unroll
+            for (int i = 0; i < MOE_ROUTE_TOK; i++)
+                if (i < nt) acc[i] = fmaf(ld_f(x + (size_t)(tb + i) * D + k), wk, acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < MOE_ROUTE_TOK; i++) {
+            const float v = warp_sum(acc[i]);
+            if (lane == 0 && i < nt) moe_sm[(size_t)i * 2 * N + n] = v;
+        }
+    }
+    __syncthreads();
+    if (warp >= nt) return;
+    const int t = tb + warp;
     float* s = moe_sm + (size_t)warp * 2 * N;
     float* c = s + N;
-    const T* xr = x + (size_t)t * D;
-    for (int n = 0; n < N; n++) {
-        const float* w = router + (size_t)n * D;
-        float acc = 0.0f;
-        for (int k = lane; k < D; k += 32) acc = fmaf(ld_f(xr + k), w[k], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) s[n] = acc;
-    }
-    __syncwarp();
     float mx = -INFINITY;
     for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
     mx = warp_max(mx);
@@ -95,8 +112,9 @@ extern "C" int ri_moe_route(const void* x, const float* router, const float* cor
     if (tokens == 0) return 0;
     RI_REQUIRE(tokens > 0 && D > 0 && N > 0 && top > 0 && top <= N, "moe_route: bad sizes (top %d of %d)", top, N);
     RI_REQUIRE(N <= 4096, "moe_route: %d router outputs (up to 4096 are built)", N);
-    const size_t smem = (size_t)MOE_ROUTE_WARPS * 2 * N * sizeof(float);
-    const dim3 grid((tokens + MOE_ROUTE_WARPS - 1) / MOE_ROUTE_WARPS);
+    static_assert(MOE_ROUTE_TOK <= MOE_ROUTE_WARPS, "a warp per token for the choice");
+    const size_t smem = (size_t)MOE_ROUTE_TOK * 2 * N * sizeof(float);
+    const dim3 grid((tokens + MOE_ROUTE_TOK - 1) / MOE_ROUTE_TOK);
     cudaError_t e = cudaSuccess;
     if (dtype == RI_DTYPE_F32) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -117,7 +135,7 @@ extern "C" int ri_moe_route(const void* x, const float* router, const float* cor
 // meta[0] = number of tiles, meta[1] = number of rows in perm.  tiles [max_tiles][3].
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ idx, int* __restrict__ perm, int* __restrict__ tiles, int* __restrict__ meta,
-                int pairs, int E, int max_tiles) {
+                int pairs, int E, int max_tiles, int bm) {
     extern __shared__ int plan_sm[];                  // counts [E], offsets [E + 1], cursors [E]
     int* counts = plan_sm;
     int* offsets = counts + E;
@@ -135,10 +153,10 @@ moe_plan_kernel(const int* __restrict__ idx, int* __restrict__ perm, int* __rest
         int off = 0, n = 0;
         for (int e = 0; e < E; e++) {
             offsets[e] = off;
-            for (int r = 0; r < counts[e] && n < max_tiles; r += MOE_BM) {
+            for (int r = 0; r < counts[e] && n < max_tiles; r += bm) {
                 tiles[3 * n] = e;
                 tiles[3 * n + 1] = off + r;
-                tiles[3 * n + 2] = min(MOE_BM, counts[e] - r);
+                tiles[3 * n + 2] = min(bm, counts[e] - r);
                 n++;
             }
             off += counts[e];
@@ -154,15 +172,17 @@ moe_plan_kernel(const int* __restrict__ idx, int* __restrict__ perm, int* __rest
     }
 }
 
-extern "C" int ri_moe_max_tiles(int pairs, int E) { return (pairs + MOE_BM - 1) / MOE_BM + E; }
+// bm: rows per tile, MOE_BM (32) or MOE_BM_WIDE (64: many pairs per expert, bfloat16 with 16-byte rows)
+extern "C" int ri_moe_max_tiles(int pairs, int E, int bm) { return (pairs + bm - 1) / bm + E; }
 
-extern "C" int ri_moe_plan(const int* idx, int* perm, int* tiles, int* meta, int pairs, int E, int max_tiles,
+extern "C" int ri_moe_plan(const int* idx, int* perm, int* tiles, int* meta, int pairs, int E, int max_tiles, int bm,
                            cudaStream_t stream) {
     if (pairs == 0) return 0;
-    RI_REQUIRE(pairs > 0 && E > 0 && max_tiles >= ri_moe_max_tiles(pairs, E), "moe_plan: bad sizes");
+    RI_REQUIRE(bm == MOE_BM || bm == MOE_BM_WIDE, "moe_plan: tiles of %d rows are not built", bm);
+    RI_REQUIRE(pairs > 0 && E > 0 && max_tiles >= ri_moe_max_tiles(pairs, E, bm), "moe_plan: bad sizes");
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
     RI_REQUIRE(smem <= 48 * 1024, "moe_plan: %d experts (up to 4095 are built)", E);
-    ri_launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, idx, perm, tiles, meta, pairs, E, max_tiles);
+    ri_launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, idx, perm, tiles, meta, pairs, E, max_tiles, bm);
     RI_CHECK_LAUNCH("moe_plan");
     return 0;
 }
@@ -230,14 +250,19 @@ moe_grouped_f32_kernel(const float* __restrict__ a, long long lda, const float* 
     }
 }
 
-// bfloat16: 4 warps; warp w owns columns 16 w .. 16 w + 15 of the tile and all 32 rows (2 x 2 mma tiles per k16)
-template <typename TO>
+// bfloat16: 4 warps; warp w owns columns 16 w .. 16 w + 15 of the tile and all 32 rows (2 x 2 mma tiles per k16).
+// VEC (K a multiple of 8, 16-byte aligned rows): the tiles of A and W come by cp.async through a ring of MOE_STAGES
+// stages of 64 k each, so that two stages are on their way while one is multiplied; otherwise element by element.
+#define MOE_STAGES 3
+#define MOE_BK 64
+#define MOE_PITCH (MOE_BK + 8)
+template <typename TO, bool VEC>
 __global__ void __launch_bounds__(128)
 moe_grouped_bf16_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ w, TO* __restrict__ y,
                         long long ldy, const int* __restrict__ perm, const int* __restrict__ tiles,
-                        const int* __restrict__ meta, int N, int K, int gather_div, int scatter, int vec) {
-    constexpr int BK = 32, PITCH = BK + 8;
-    __shared__ __align__(16) bf16 As[MOE_BM][PITCH], Ws[MOE_BN][PITCH];
+                        const int* __restrict__ meta, int N, int K, int gather_div, int scatter) {
+    constexpr int ST = VEC ? MOE_STAGES : 1;
+    __shared__ __align__(16) bf16 As[ST][MOE_BM][MOE_PITCH], Ws[ST][MOE_BN][MOE_PITCH];
     __shared__ int s_in[MOE_BM], s_out[MOE_BM];
     pdl_trigger();
     pdl_wait();
@@ -255,47 +280,37 @@ moe_grouped_bf16_kernel(const bf16* __restrict__ a, long long lda, const bf16* _
     const int quad = lane >> 2, qc = lane & 3;
     float acc[2][2][4] = {};
     const bf16 zero = __float2bfloat16_rn(0.0f);
-    for (int k0 = 0; k0 < K; k0 += BK) {
-        if (vec) {
-            {   // 32 rows x 4 pieces of 8 elements
-                const int r = threadIdx.x / 4, kc = (threadIdx.x % 4) * 8;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (r < rows && k0 + kc < K) v = *reinterpret_cast<const uint4*>(a + (size_t)s_in[r] * lda + k0 + kc);
-                *reinterpret_cast<uint4*>(&As[r][kc]) = v;
-            }
+    auto copy_stage = [&](int st, int k0) {        // VEC: 16-byte pieces, zeros past the tile's rows, N and K
 #pragma unroll
-            for (int pass = 0; pass < 2; pass++) {
-                const int i = threadIdx.x + pass * 128;
-                const int n = i / 4, kc = (i % 4) * 8;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (n0 + n < N && k0 + kc < K) v = *reinterpret_cast<const uint4*>(we + (size_t)(n0 + n) * K + k0 + kc);
-                *reinterpret_cast<uint4*>(&Ws[n][kc]) = v;
-            }
-        } else {
-            for (int i = threadIdx.x; i < MOE_BM * BK; i += blockDim.x) {
-                const int r = i / BK, k = i % BK;
-                As[r][k] = (r < rows && k0 + k < K) ? a[(size_t)s_in[r] * lda + k0 + k] : zero;
-            }
-            for (int i = threadIdx.x; i < MOE_BN * BK; i += blockDim.x) {
-                const int n = i / BK, k = i % BK;
-                Ws[n][k] = (n0 + n < N && k0 + k < K) ? we[(size_t)(n0 + n) * K + k0 + k] : zero;
-            }
+        for (int pass = 0; pass < 2; pass++) {
+            const int i = threadIdx.x + pass * 128;
+            const int r = i / 8, kc = (i % 8) * 8;
+            const bool ok = r < rows && k0 + kc < K;
+            cp_async16(&As[st][r][kc], ok ? a + (size_t)s_in[r] * lda + k0 + kc : a, ok);
         }
-        __syncthreads();
 #pragma unroll
-        for (int kk = 0; kk < BK; kk += 16) {
+        for (int pass = 0; pass < 4; pass++) {
+            const int i = threadIdx.x + pass * 128;
+            const int n = i / 8, kc = (i % 8) * 8;
+            const bool ok = n0 + n < N && k0 + kc < K;
+            cp_async16(&Ws[st][n][kc], ok ? we + (size_t)(n0 + n) * K + k0 + kc : we, ok);
+        }
+    };
+    auto multiply = [&](int st) {
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; kk += 16) {
             unsigned af[2][4], bfr[2][2];
 #pragma unroll
             for (int mi = 0; mi < 2; mi++) {
-                af[mi][0] = *reinterpret_cast<const unsigned*>(&As[mi * 16 + quad][kk + qc * 2]);
-                af[mi][1] = *reinterpret_cast<const unsigned*>(&As[mi * 16 + quad + 8][kk + qc * 2]);
-                af[mi][2] = *reinterpret_cast<const unsigned*>(&As[mi * 16 + quad][kk + qc * 2 + 8]);
-                af[mi][3] = *reinterpret_cast<const unsigned*>(&As[mi * 16 + quad + 8][kk + qc * 2 + 8]);
+                af[mi][0] = *reinterpret_cast<const unsigned*>(&As[st][mi * 16 + quad][kk + qc * 2]);
+                af[mi][1] = *reinterpret_cast<const unsigned*>(&As[st][mi * 16 + quad + 8][kk + qc * 2]);
+                af[mi][2] = *reinterpret_cast<const unsigned*>(&As[st][mi * 16 + quad][kk + qc * 2 + 8]);
+                af[mi][3] = *reinterpret_cast<const unsigned*>(&As[st][mi * 16 + quad + 8][kk + qc * 2 + 8]);
             }
 #pragma unroll
             for (int ni = 0; ni < 2; ni++) {
-                bfr[ni][0] = *reinterpret_cast<const unsigned*>(&Ws[warp * 16 + ni * 8 + quad][kk + qc * 2]);
-                bfr[ni][1] = *reinterpret_cast<const unsigned*>(&Ws[warp * 16 + ni * 8 + quad][kk + qc * 2 + 8]);
+                bfr[ni][0] = *reinterpret_cast<const unsigned*>(&Ws[st][warp * 16 + ni * 8 + quad][kk + qc * 2]);
+                bfr[ni][1] = *reinterpret_cast<const unsigned*>(&Ws[st][warp * 16 + ni * 8 + quad][kk + qc * 2 + 8]);
             }
 #pragma unroll
             for (int mi = 0; mi < 2; mi++)
@@ -303,7 +318,37 @@ moe_grouped_bf16_kernel(const bf16* __restrict__ a, long long lda, const bf16* _
                 for (int ni = 0; ni < 2; ni++)
                     mma_bf16(acc[mi][ni], af[mi][0], af[mi][1], af[mi][2], af[mi][3], bfr[ni][0], bfr[ni][1]);
         }
-        __syncthreads();
+    };
+    const int nk = (K + MOE_BK - 1) / MOE_BK;
+    if (VEC) {
+        for (int st = 0; st < MOE_STAGES - 1; st++) {
+            if (st < nk) copy_stage(st, st * MOE_BK);
+            cp_async_commit();
+        }
+        for (int it = 0; it < nk; it++) {
+            cp_async_wait<MOE_STAGES - 2>();
+            __syncthreads();                         // stage `it` has landed for everyone; the stage of it - 1 is free
+            const int ahead = it + MOE_STAGES - 1;
+            if (ahead < nk) copy_stage(ahead % MOE_STAGES, ahead * MOE_BK);
+            cp_async_commit();
+            multiply(it % MOE_STAGES);
+        }
+        cp_async_wait<0>();
+    } else {
+        for (int it = 0; it < nk; it++) {
+            const int k0 = it * MOE_BK;
+            for (int i = threadIdx.x; i < MOE_BM * MOE_BK; i += blockDim.x) {
+                const int r = i / MOE_BK, k = i % MOE_BK;
+                As[0][r][k] = (r < rows && k0 + k < K) ? a[(size_t)s_in[r] * lda + k0 + k] : zero;
+            }
+            for (int i = threadIdx.x; i < MOE_BN * MOE_BK; i += blockDim.x) {
+                const int n = i / MOE_BK, k = i % MOE_BK;
+                Ws[0][n][k] = (n0 + n < N && k0 + k < K) ? we[(size_t)(n0 + n) * K + k0 + k] : zero;
+            }
+            __syncthreads();
+            multiply(0);
+            __syncthreads();
+        }
     }
 #pragma unroll
     for (int mi = 0; mi < 2; mi++)
@@ -317,11 +362,102 @@ moe_grouped_bf16_kernel(const bf16* __restrict__ a, long long lda, const bf16* _
             }
 }
 
+// Tiles of 64 rows for steps with many pairs per expert (prompts): 2 x 2 warps, each 32 rows x 32 columns (2 x 4 mma
+// tiles per k16), fragments by ldmatrix (4 instructions for 8 products), the same ring of cp.async stages in dynamic
+// shared memory.  Only with 16-byte rows (K a multiple of 8).
+#define MOE_WIDE_SMEM (MOE_STAGES * (MOE_BM_WIDE + MOE_BN) * MOE_PITCH * 2)
+template <typename TO>
+__global__ void __launch_bounds__(128)
+moe_grouped_bf16_wide_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ w, TO* __restrict__ y,
+                             long long ldy, const int* __restrict__ perm, const int* __restrict__ tiles,
+                             const int* __restrict__ meta, int N, int K, int gather_div, int scatter) {
+    extern __shared__ __align__(16) unsigned char moe_wide_sm[];
+    bf16 (*As)[MOE_BM_WIDE][MOE_PITCH] = reinterpret_cast<bf16 (*)[MOE_BM_WIDE][MOE_PITCH]>(moe_wide_sm);
+    bf16 (*Ws)[MOE_BN][MOE_PITCH] =
+        reinterpret_cast<bf16 (*)[MOE_BN][MOE_PITCH]>(moe_wide_sm + MOE_STAGES * MOE_BM_WIDE * MOE_PITCH * 2);
+    __shared__ int s_in[MOE_BM_WIDE], s_out[MOE_BM_WIDE];
+    pdl_trigger();
+    pdl_wait();
+    if ((int)blockIdx.x >= meta[0]) return;
+    const int e = tiles[3 * blockIdx.x], r0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+    const int n0 = blockIdx.y * MOE_BN;
+    for (int i = threadIdx.x; i < MOE_BM_WIDE; i += blockDim.x) {
+        const int p = i < rows ? perm[r0 + i] : 0;
+        s_in[i] = gather_div > 0 ? p / gather_div : r0 + i;
+        s_out[i] = scatter ? p : r0 + i;
+    }
+    __syncthreads();
+    const bf16* we = w + (size_t)e * N * K;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wm = warp >> 1, wn = warp & 1;
+    const int quad = lane >> 2, qc = lane & 3;
+    float acc[2][4][4] = {};
+    auto copy_stage = [&](int st, int k0) {
+#pragma unroll
+        for (int pass = 0; pass < 4; pass++) {
+            const int i = threadIdx.x + pass * 128;
+            const int r = i / 8, kc = (i % 8) * 8;
+            const bool ok = r < rows && k0 + kc < K;
+            cp_async16(&As[st][r][kc], ok ? a + (size_t)s_in[r] * lda + k0 + kc : a, ok);
+        }
+#pragma unroll
+        for (int pass = 0; pass < 4; pass++) {
+            const int i = threadIdx.x + pass * 128;
+            const int n = i / 8, kc = (i % 8) * 8;
+            const bool ok = n0 + n < N && k0 + kc < K;
+            cp_async16(&Ws[st][n][kc], ok ? we + (size_t)(n0 + n) * K + k0 + kc : we, ok);
+        }
+    };
+    const int nk = (K + MOE_BK - 1) / MOE_BK;
+    for (int st = 0; st < MOE_STAGES - 1; st++) {
+        if (st < nk) copy_stage(st, st * MOE_BK);
+        cp_async_commit();
+    }
+    for (int it = 0; it < nk; it++) {
+        cp_async_wait<MOE_STAGES - 2>();
+        __syncthreads();
+        const int ahead = it + MOE_STAGES - 1;
+        if (ahead < nk) copy_stage(ahead % MOE_STAGES, ahead * MOE_BK);
+        cp_async_commit();
+        const int st = it % MOE_STAGES;
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; kk += 16) {
+            unsigned af[2][4], bfr[4][2];
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++)
+                ldmatrix_x4(af[mi][0], af[mi][1], af[mi][2], af[mi][3],
+                            &As[st][wm * 32 + mi * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+            for (int np = 0; np < 2; np++)          // two n8 tiles per instruction: (b0, b1) of the first, then of the second
+                ldmatrix_x4(bfr[2 * np][0], bfr[2 * np][1], bfr[2 * np + 1][0], bfr[2 * np + 1][1],
+                            &Ws[st][wn * 32 + np * 16 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+                for (int ni = 0; ni < 4; ni++)
+                    mma_bf16(acc[mi][ni], af[mi][0], af[mi][1], af[mi][2], af[mi][3], bfr[ni][0], bfr[ni][1]);
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+        for (int ni = 0; ni < 4; ni++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int r = wm * 32 + mi * 16 + quad + (c >> 1) * 8;
+                const int n = n0 + wn * 32 + ni * 8 + qc * 2 + (c & 1);
+                if (r < rows && n < N) moe_store(y + (size_t)s_out[r] * ldy + n, acc[mi][ni][c]);
+            }
+}
+
 // a [rows, lda] and w [E, N, K] in the compute type; y [.., ldy] float32 (out_f32) or the compute type
+// bm: the tile height that the plan was made with
 extern "C" int ri_moe_grouped_linear(const void* a, long long lda, const void* w, void* y, long long ldy, const int* perm,
-                                     const int* tiles, const int* meta, int max_tiles, int N, int K, int gather_div,
+                                     const int* tiles, const int* meta, int max_tiles, int bm, int N, int K, int gather_div,
                                      int scatter, int out_f32, int dtype, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
+    RI_REQUIRE(bm == MOE_BM || (bm == MOE_BM_WIDE && dtype == RI_DTYPE_BF16), "moe_grouped_linear: tiles of %d rows", bm);
     RI_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && gather_div >= 0, "moe_grouped_linear: bad sizes");
     const dim3 grid(max_tiles, (N + MOE_BN - 1) / MOE_BN);
     RI_REQUIRE(grid.y <= 65535, "moe_grouped_linear: %d outputs are too many for one launch", N);
@@ -331,12 +467,29 @@ extern "C" int ri_moe_grouped_linear(const void* a, long long lda, const void* w
                       (float*)y, ldy, perm, tiles, meta, N, K, gather_div, scatter);
     } else if (dtype == RI_DTYPE_BF16) {
         const int vec = (K % 8 == 0 && lda % 8 == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0) ? 1 : 0;
-        if (out_f32)
-            ri_launch_pdl(moe_grouped_bf16_kernel<float>, grid, dim3(128), 0, stream, (const bf16*)a, lda, (const bf16*)w,
-                          (float*)y, ldy, perm, tiles, meta, N, K, gather_div, scatter, vec);
-        else
-            ri_launch_pdl(moe_grouped_bf16_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)a, lda, (const bf16*)w,
-                          (bf16*)y, ldy, perm, tiles, meta, N, K, gather_div, scatter, vec);
+        if (bm == MOE_BM_WIDE) {
+            RI_REQUIRE(vec, "moe_grouped_linear: tiles of 64 rows need rows of whole 16-byte pieces");
+            cudaError_t e1 = cudaFuncSetAttribute(moe_grouped_bf16_wide_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_WIDE_SMEM);
+            cudaError_t e2 = cudaFuncSetAttribute(moe_grouped_bf16_wide_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_WIDE_SMEM);
+            if (e1 != cudaSuccess || e2 != cudaSuccess) RI_FAIL(-1, "moe_grouped_linear: shared memory for the wide tiles");
+            if (out_f32)
+                ri_launch_pdl(moe_grouped_bf16_wide_kernel<float>, grid, dim3(128), MOE_WIDE_SMEM, stream, (const bf16*)a, lda,
+                              (const bf16*)w, (float*)y, ldy, perm, tiles, meta, N, K, gather_div, scatter);
+            else
+                ri_launch_pdl(moe_grouped_bf16_wide_kernel<bf16>, grid, dim3(128), MOE_WIDE_SMEM, stream, (const bf16*)a, lda,
+                              (const bf16*)w, (bf16*)y, ldy, perm, tiles, meta, N, K, gather_div, scatter);
+            RI_CHECK_LAUNCH("moe_grouped_linear");
+            return 0;
+        }
+#define MOE_GO(TO, VEC)                                                                                                  \
+        ri_launch_pdl(moe_grouped_bf16_kernel<TO, VEC>, grid, dim3(128), 0, stream, (const bf16*)a, lda, (const bf16*)w,    \
+                      (TO*)y, ldy, perm, tiles, meta, N, K, gather_div, scatter)
+        if (out_f32) {
+            if (vec) MOE_GO(float, true); else MOE_GO(float, false);
+        } else {
+            if (vec) MOE_GO(bf16, true); else MOE_GO(bf16, false);
+        }
+#undef MOE_GO
     } else RI_FAIL(-1, "moe_grouped_linear: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("moe_grouped_linear");
     return 0;
@@ -350,7 +503,7 @@ moe_combine_kernel(const float* __restrict__ pair_out, const int* __restrict__ i
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) {
         float acc = 0.0f;
         for (int j = 0; j < top; j++) {
             const int e = idx[(size_t)t * top + j];
@@ -366,11 +519,12 @@ extern "C" int ri_moe_combine(const float* pair_out, const int* idx, const float
                               void* y, int tokens, int D, int top, int E, int dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
     RI_REQUIRE(tokens > 0 && D > 0 && top > 0, "moe_combine: bad sizes");
+    const dim3 grid(tokens, tokens >= 512 ? 1 : (D + 255) / 256 > 64 ? 64 : (D + 255) / 256);    // few tokens: a row over several blocks
     if (dtype == RI_DTYPE_F32)
-        ri_launch_pdl(moe_combine_kernel<float>, dim3(tokens), dim3(256), 0, stream, pair_out, idx, weight, (const float*)x,
+        ri_launch_pdl(moe_combine_kernel<float>, grid, dim3(256), 0, stream, pair_out, idx, weight, (const float*)x,
                       (const float*)extra, (float*)y, D, top, E);
     else if (dtype == RI_DTYPE_BF16)
-        ri_launch_pdl(moe_combine_kernel<bf16>, dim3(tokens), dim3(256), 0, stream, pair_out, idx, weight, (const bf16*)x,
+        ri_launch_pdl(moe_combine_kernel<bf16>, grid, dim3(256), 0, stream, pair_out, idx, weight, (const bf16*)x,
                       (const bf16*)extra, (bf16*)y, D, top, E);
     else RI_FAIL(-1, "moe_combine: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("moe_combine");

@@ -30,12 +30,12 @@ _SIGNATURES = {
     ("streams", "ri_stream_norm2"): [_P] * 13 + [_I, _I, _I, _F, _I, _I, _P],
     ("pair_embedding", "ri_embed_pair_hash"): [_P] * 9 + [_I, _I, _I, _I, _I, _L, _L, _I, _I, _P, _P],
     ("delta_rule", "ri_short_conv"): [_P, _L, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    ("delta_rule", "ri_delta_rule_recurrent"): [_P, _I, _I, _I, _I, _P, _L, _I, _P, _P, _P, _F, _P, _P, _P, _P] + [_I] * 7 + [_P],
+    ("delta_rule", "ri_delta_rule_recurrent"): [_P, _I, _I, _I, _I, _P, _L, _I, _P, _P, _P, _F] + [_P] * 6 + [_I] * 8 + [_P],
     ("elementwise", "ri_gated_act"): [_P, _P, _I, _I, _I, _I, _F, _F, _I, _P],
     ("elementwise", "ri_scale_f32"): [_P, _L, _F, _P],
     ("moe", "ri_moe_route"): [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
-    ("moe", "ri_moe_plan"): [_P, _P, _P, _P, _I, _I, _I, _P],
-    ("moe", "ri_moe_grouped_linear"): [_P, _L, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    ("moe", "ri_moe_plan"): [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    ("moe", "ri_moe_grouped_linear"): [_P, _L, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     ("moe", "ri_moe_combine"): [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     ("rope_kv", "ri_qk_norm_rope_append_pairs"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 10 + [_P, _P],
     ("latent_attention", "ri_latent_prep"): [_P, _L, _I, _I] + [_P] * 8 + [_F, _P] + [_I] * 11 + [_P, _P],
@@ -56,7 +56,7 @@ _SIGNATURES = {
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny_act"): [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
-    ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _P],
+    ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _I, _P, _P],
 }
 DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
@@ -755,12 +755,12 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
     _need(seq_len, "seq_len", torch.int32, (seqs,))
     out = torch.empty_like(q)
-    if Dh in TCGEN05_HEAD_DIMS and not _NO_TCGEN05 and sink is None and not chunk:
-        # head sizes of 64 and 128: the tcgen05 / tensor-memory kernel (it has no sink term: those go below)
+    if Dh in TCGEN05_HEAD_DIMS and not _NO_TCGEN05:
+        # head sizes of 64 and 128: the tcgen05 / tensor-memory kernel
         _call("attention_prefill_tc", "ri_attention_prefill_tc", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
               out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
-              q.shape[0], seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
-              error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+              q.shape[0], seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale),
+              _mask(window, chunk), _sink(sink, H), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
         return out
     _call("attention_prefill", "ri_attention_prefill", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
@@ -909,7 +909,8 @@ def delta_rule_recurrent(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, 
     S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q, with q and k made unit vectors (q also times
     ``qscale``), g = exp(-exp(a_log[h]) softplus(z + dt_bias)) per key channel and beta = sigmoid of column
     ``beta_col + h`` of ``proj``.  ``qkv`` [tokens, C] float32 holds q, k, v from ``q_col``, ``k_col``, ``v_col``;
-    ``z`` [tokens, H*dim] in the compute dtype.  Returns o [tokens, H, vdim] float32."""
+    ``z`` [tokens, H*dim] in the compute dtype.  The q and k columns of ``qkv`` are made unit vectors in place.
+    Returns o [tokens, H, vdim] float32."""
     _need(qkv, "qkv", torch.float32)
     tokens, C = qkv.shape
     _need(proj, "proj")
@@ -925,10 +926,13 @@ def delta_rule_recurrent(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, 
     _need(seq_slot, "seq_slot", torch.int32, (seqs,))
     _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
     o = torch.empty((tokens, heads, vdim), dtype=torch.float32, device=qkv.device)
+    decay = torch.empty((tokens, heads * dim), dtype=torch.float32, device=qkv.device)
+    beta = torch.empty((tokens, heads + qk_heads), dtype=torch.float32, device=qkv.device)
     _call("delta_rule", "ri_delta_rule_recurrent", qkv.data_ptr(), C, int(q_col), int(k_col), int(v_col), proj.data_ptr(),
-          proj.shape[1], int(beta_col), z.data_ptr(), dt_bias.data_ptr(), a_log.data_ptr(), float(qscale), state.data_ptr(),
-          o.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seqs, heads, qk_heads, dim, vdim,
-          1 if single and tokens == seqs else 0, _code(proj.dtype), _stream())
+          proj.shape[1], int(beta_col), z.data_ptr(), dt_bias.data_ptr(), a_log.data_ptr(), float(qscale), decay.data_ptr(),
+          beta.data_ptr(), state.data_ptr(), o.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), tokens, seqs, heads,
+          qk_heads, dim, vdim, 1 if single and tokens == seqs else 0, _code(proj.dtype), _stream())
+    add_launches(1)
     return o
 
 
@@ -981,27 +985,32 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, t
     return idx, weight
 
 
-def moe_plan(idx: torch.Tensor, experts: int):
+MOE_TILE_ROWS, MOE_TILE_ROWS_WIDE = 32, 64
+
+
+def moe_plan(idx: torch.Tensor, experts: int, wide: bool = False):
     """The step's (token, choice) pairs grouped by expert for the grouped products: (perm int32 [pairs], tiles int32
-    [max_tiles, 3] of (expert, first row, rows), meta int32 [2] = (tiles, rows)); choices >= ``experts`` are left out.
-    Everything stays on the device."""
+    [max_tiles, 3] of (expert, first row, rows), meta int32 [2] = (tiles, rows), rows per tile); choices >= ``experts``
+    are left out.  ``wide``: tiles of 64 rows instead of 32 (many pairs per expert; bfloat16 products whose rows are whole
+    16-byte pieces).  Everything stays on the device."""
     _need(idx, "idx", torch.int32)
     pairs = idx.numel()
+    bm = MOE_TILE_ROWS_WIDE if wide else MOE_TILE_ROWS
     _, lib = _fn("moe", "ri_moe_plan")
-    max_tiles = int(lib.ri_moe_max_tiles(int(pairs), int(experts)))
+    max_tiles = int(lib.ri_moe_max_tiles(int(pairs), int(experts), bm))
     perm = torch.empty(max(pairs, 1), dtype=torch.int32, device=idx.device)
     tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=idx.device)
     meta = torch.empty(2, dtype=torch.int32, device=idx.device)
     _call("moe", "ri_moe_plan", idx.data_ptr(), perm.data_ptr(), tiles.data_ptr(), meta.data_ptr(), pairs, int(experts),
-          max_tiles, _stream())
-    return perm, tiles, meta
+          max_tiles, bm, _stream())
+    return perm, tiles, meta, bm
 
 
 def moe_grouped_linear(a: torch.Tensor, w: torch.Tensor, plan, rows_out: int, gather_div: int = 0, scatter: bool = False,
                        out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y[out(r)] = w[e] a[in(r)] for every row r of the plan's tiles; ``w`` [E, N, K]; in(r) = perm[r] // gather_div
     (``gather_div`` > 0) or r; out(r) = perm[r] (``scatter``) or r.  Rows that no tile covers are not written."""
-    perm, tiles, meta = plan
+    perm, tiles, meta, bm = plan
     _need(a, "a")
     _need(w, "w", a.dtype)
     E, N, K = w.shape
@@ -1012,7 +1021,7 @@ def moe_grouped_linear(a: torch.Tensor, w: torch.Tensor, plan, rows_out: int, ga
         raise KernelError("moe_grouped_linear: the result is float32 or the compute dtype")
     y = torch.empty((rows_out, N), dtype=out_dtype, device=a.device)
     _call("moe", "ri_moe_grouped_linear", a.data_ptr(), a.stride(0), w.data_ptr(), y.data_ptr(), N, perm.data_ptr(),
-          tiles.data_ptr(), meta.data_ptr(), tiles.shape[0], N, K, int(gather_div), 1 if scatter else 0,
+          tiles.data_ptr(), meta.data_ptr(), tiles.shape[0], int(bm), N, K, int(gather_div), 1 if scatter else 0,
           1 if out_dtype == torch.float32 else 0, _code(a.dtype), _stream())
     return y
 

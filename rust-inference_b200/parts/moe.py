@@ -65,7 +65,10 @@ class MixtureOfExperts(FeedForward):
         T = x.shape[0]
         with section("moe router"):
             idx, weight = ops.moe_route(x, self.router, self.correction, s.top)
-            plan = ops.moe_plan(idx, s.experts)
+            # many pairs per expert (a prompt): tiles of 64 rows, where the bfloat16 kernel for them takes the sizes
+            wide = (x.dtype == torch.bfloat16 and T * s.top >= 48 * s.experts and s.hidden_size % 8 == 0
+                    and ex.intermediate_size % 8 == 0)
+            plan = ops.moe_plan(idx, s.experts, wide)
         with section("moe experts"):
             gu = ops.moe_grouped_linear(x, self.gate_up, plan, T * s.top, gather_div=s.top)
             act = ops.gated_act(gu, ex.gate, None, ex.limit, ex.alpha)

@@ -345,7 +345,7 @@ def moe_route(x, router, correction, top):
     return idx, w / (w.sum(-1, keepdim=True) + 1e-20)
 
 
-def moe_plan(idx, experts):
+def moe_plan(idx, experts, wide=False):
     flat = idx.flatten()
     perm = torch.tensor([p for e in range(experts) for p in torch.nonzero(flat == e).flatten().tolist()], dtype=torch.int32)
     tiles = torch.tensor([[e, 0, 0] for e in range(experts)], dtype=torch.int32)
@@ -354,11 +354,11 @@ def moe_plan(idx, experts):
         n = int((flat == e).sum())
         tiles[e, 1], tiles[e, 2] = off, n
         off += n
-    return perm, tiles, torch.tensor([experts, off], dtype=torch.int32)
+    return perm, tiles, torch.tensor([experts, off], dtype=torch.int32), 0
 
 
 def moe_grouped_linear(a, w, plan, rows_out, gather_div=0, scatter=False, out_dtype=None):
-    perm, tiles, meta = plan
+    perm, tiles, meta, _ = plan
     y = torch.zeros(rows_out, w.shape[1], dtype=out_dtype or a.dtype)
     for e, r0, n in tiles[:int(meta[0])].tolist():
         for r in range(r0, r0 + n):

@@ -136,8 +136,8 @@ def test_delta_rule_against_the_plain_recurrence(H, G, dim, vdim, dtype):
     dt_bias, a_log = _t(rng.uniform(-3, 1, H * dim)), _t(rng.uniform(-2, 0.5, H))
     tok_seq, seq_start = _tables(lengths)
     state = torch.zeros((4, H, dim, vdim), device=DEV)
-    o = ops.delta_rule_recurrent(qkv, 0, G * dim, 2 * G * dim, proj, 3, z, dt_bias, a_log, dim ** -0.5, state, _i(slots),
-                                 seq_start, H, G, dim, vdim)
+    o = ops.delta_rule_recurrent(qkv.clone(), 0, G * dim, 2 * G * dim, proj, 3, z, dt_bias, a_log, dim ** -0.5, state, _i(slots),
+                                 seq_start, H, G, dim, vdim)                   # (the call makes q and k unit vectors in place)
     q = _np(qkv)[:, :G * dim].reshape(T, G, dim)
     k = _np(qkv)[:, G * dim:2 * G * dim].reshape(T, G, dim)
     v = _np(qkv)[:, 2 * G * dim:].reshape(T, H, vdim)
@@ -160,7 +160,7 @@ def test_delta_rule_against_the_plain_recurrence(H, G, dim, vdim, dtype):
         outs, at = [], 0
         for c in cuts:
             _, ss = _tables([c])
-            outs.append(ops.delta_rule_recurrent(qkv[at:at + c].contiguous(), 0, G * dim, 2 * G * dim, proj[at:at + c].contiguous(), 3,
+            outs.append(ops.delta_rule_recurrent(qkv[at:at + c].clone(), 0, G * dim, 2 * G * dim, proj[at:at + c].contiguous(), 3,
                                                  z[at:at + c].contiguous(), dt_bias, a_log, dim ** -0.5, st2, _i([1]), ss, H, G, dim,
                                                  vdim, single=(c == 1)))
             at += c
