@@ -24,43 +24,72 @@
 #define MOE_BN 64
 #define MOE_ROUTE_WARPS 4
 
-// A block takes MOE_ROUTE_TOK tokens: its warps share the router's outputs among them (warp w takes n = w, w + warps, ..)
-// and compute an output's logit for all the block's tokens at once, so a row of the router is read once per block; then a
-// warp per token does the softmax and the choice.  A token's sums do not depend on the tokens beside it.
-#define MOE_ROUTE_TOK 4
+// A warp per token.  The logits are taken four router outputs at a time: a lane walks its own k (four neighbouring ones
+// per trip with 16-byte loads where the rows allow it, else one) and keeps four sums, so that twenty loads are on their
+// way together; a sum's order depends on the row's size alone.  Then the warp does the softmax and the choice.
+__device__ __forceinline__ float4 moe_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 moe_ld4(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(32 * MOE_ROUTE_WARPS)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
-                 int* __restrict__ idx, float* __restrict__ weight, int tokens, int D, int N, int top) {
-    extern __shared__ float moe_sm[];                 // per token of the block: scores [N], choice scores [N]
+                 int* __restrict__ idx, float* __restrict__ weight, int tokens, int D, int N, int top, int vec) {
+    extern __shared__ float moe_sm[];                 // per warp: scores [N], choice scores [N]
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int tb = blockIdx.x * MOE_ROUTE_TOK;
-    const int nt = min(MOE_ROUTE_TOK, tokens - tb);
-    for (int n = warp; n < N; n += MOE_ROUTE_WARPS) {
-        const float* w = router + (size_t)n * D;
-        float acc[MOE_ROUTE_TOK];
-#pragma unroll
-        for (int i = 0; i < MOE_ROUTE_TOK; i++) acc[i] = 0.0f;
-#pragma unroll 4
-        for (int k = lane; k < D; k += 32) {
-            const float wk = w[k];
-#pragma unroll
-            for (int i = 0; i < MOE_ROUTE_TOK; i++)
-                if (i < nt) acc[i] = fmaf(ld_f(x + (size_t)(tb + i) * D + k), wk, acc[i]);
-        }
-#pragma unroll
-        for (int i = 0; i < MOE_ROUTE_TOK; i++) {
-            const float v = warp_sum(acc[i]);
-            if (lane == 0 && i < nt) moe_sm[(size_t)i * 2 * N + n] = v;
-        }
-    }
-    __syncthreads();
-    if (warp >= nt) return;
-    const int t = tb + warp;
+    const int t = blockIdx.x * MOE_ROUTE_WARPS + warp;
+    if (t >= tokens) return;
     float* s = moe_sm + (size_t)warp * 2 * N;
     float* c = s + N;
+    const T* xr = x + (size_t)t * D;
+    for (int n0 = 0; n0 < N; n0 += 4) {
+        const float* w[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) w[j] = router + (size_t)min(n0 + j, N - 1) * D;     // past the last output: its sum is dropped
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (vec) {
+            // four trips' loads (twenty of them) are issued before the first product needs one: the loop is written out so
+            const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int k0 = 4 * lane; k0 < D; k0 += 4 * 128) {
+                float4 xv[4], wv[4][4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int k = k0 + 128 * u;
+                    const bool ok = k < D;
+                    xv[u] = ok ? moe_ld4(xr + k) : zero4;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) wv[u][j] = ok ? *reinterpret_cast<const float4*>(w[j] + k) : zero4;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        acc[j] = fmaf(xv[u].x, wv[u][j].x, acc[j]);
+                        acc[j] = fmaf(xv[u].y, wv[u][j].y, acc[j]);
+                        acc[j] = fmaf(xv[u].z, wv[u][j].z, acc[j]);
+                        acc[j] = fmaf(xv[u].w, wv[u][j].w, acc[j]);
+                    }
+            }
+        } else {
+#pragma unroll 4
+            for (int k = lane; k < D; k += 32) {
+                const float xv = ld_f(xr + k);
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[j] = fmaf(xv, w[j][k], acc[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float v = warp_sum(acc[j]);
+            if (lane == 0 && n0 + j < N) s[n0 + j] = v;
+        }
+    }
+    __syncwarp();
     float mx = -INFINITY;
     for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
     mx = warp_max(mx);
@@ -107,25 +136,126 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
         for (int j = 0; j < top; j++) weight[(size_t)t * top + j] /= picked_sum + 1e-20f;
 }
 
+// The same with a block of 1,024 threads per token, for routers small enough that all their partial sums fit in shared
+// memory: a warp takes (output, segment of 128 k) items, so the whole router is asked for at once instead of row after
+// row (one trip to memory instead of dozens: the warp-per-token form took 75 us whatever the number of tokens); a
+// segment's sum is the warp's tree, an output's logit the sum of its segments in ascending order.
+#define MOE_ROUTE_WIDE_THREADS 1024
+#define MOE_ROUTE_WIDE_ITEMS 8192
+template <typename T>
+__global__ void __launch_bounds__(MOE_ROUTE_WIDE_THREADS)
+moe_route_wide_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
+                      int* __restrict__ idx, float* __restrict__ weight, int D, int N, int top) {
+    extern __shared__ float moe_sm[];                 // partial sums [N][segs], scores [N], choice scores [N]
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x;
+    const int segs = (D + 127) / 128;
+    float* part = moe_sm;
+    float* s = part + (size_t)N * segs;
+    float* c = s + N;
+    const T* xr = x + (size_t)t * D;
+    const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int item = warp; item < N * segs; item += MOE_ROUTE_WIDE_THREADS / 32) {
+        const int n = item / segs, k = (item - n * segs) * 128 + 4 * lane;
+        const bool ok = k < D;
+        const float4 xv = ok ? moe_ld4(xr + k) : zero4;
+        const float4 wv = ok ? *reinterpret_cast<const float4*>(router + (size_t)n * D + k) : zero4;
+        float a = xv.x * wv.x;
+        a = fmaf(xv.y, wv.y, a);
+        a = fmaf(xv.z, wv.z, a);
+        a = fmaf(xv.w, wv.w, a);
+        a = warp_sum(a);
+        if (lane == 0) part[item] = a;
+    }
+    __syncthreads();
+    for (int n = threadIdx.x; n < N; n += MOE_ROUTE_WIDE_THREADS) {
+        float a = 0.0f;
+        for (int g = 0; g < segs; g++) a += part[n * segs + g];
+        s[n] = a;
+    }
+    __syncthreads();
+    if (warp > 0) return;
+    float mx = -INFINITY;
+    for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (int n = lane; n < N; n += 32) {
+        const float e = expf(s[n] - mx);
+        s[n] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    for (int n = lane; n < N; n += 32) {
+        s[n] = s[n] / sum;
+        c[n] = s[n] + correction[n];
+    }
+    __syncwarp();
+    float picked_sum = 0.0f;
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int n = lane; n < N; n += 32)
+            if (c[n] > best) {
+                best = c[n];
+                at = n;
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) {
+                best = ob;
+                at = oa;
+            }
+        }
+        if (at >= N) at = 0;
+        if (lane == 0) {
+            idx[(size_t)t * top + j] = at;
+            weight[(size_t)t * top + j] = s[at];
+            c[at] = -INFINITY;
+        }
+        picked_sum += s[at];
+        __syncwarp();
+    }
+    if (lane == 0)
+        for (int j = 0; j < top; j++) weight[(size_t)t * top + j] /= picked_sum + 1e-20f;
+}
+
 extern "C" int ri_moe_route(const void* x, const float* router, const float* correction, int* idx, float* weight,
                             int tokens, int D, int N, int top, int dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
     RI_REQUIRE(tokens > 0 && D > 0 && N > 0 && top > 0 && top <= N, "moe_route: bad sizes (top %d of %d)", top, N);
     RI_REQUIRE(N <= 4096, "moe_route: %d router outputs (up to 4096 are built)", N);
-    static_assert(MOE_ROUTE_TOK <= MOE_ROUTE_WARPS, "a warp per token for the choice");
-    const size_t smem = (size_t)MOE_ROUTE_TOK * 2 * N * sizeof(float);
-    const dim3 grid((tokens + MOE_ROUTE_TOK - 1) / MOE_ROUTE_TOK);
+    const size_t smem = (size_t)MOE_ROUTE_WARPS * 2 * N * sizeof(float);
+    const dim3 grid((tokens + MOE_ROUTE_WARPS - 1) / MOE_ROUTE_WARPS);
+    // (which form runs depends on the sizes and addresses only, never on the batch)
+    const int vec = (D % 4 == 0 && (((uintptr_t)router | (uintptr_t)x) & 15) == 0) ? 1 : 0;
     cudaError_t e = cudaSuccess;
+    const long long items = (long long)N * ((D + 127) / 128);
+    if (vec && items <= MOE_ROUTE_WIDE_ITEMS && tokens <= 65535 * 32) {
+        const size_t sm = (size_t)(items + 2 * N) * sizeof(float);
+        if (dtype == RI_DTYPE_F32)
+            ri_launch_pdl(moe_route_wide_kernel<float>, dim3(tokens), dim3(MOE_ROUTE_WIDE_THREADS), sm, stream, (const float*)x,
+                          router, correction, idx, weight, D, N, top);
+        else if (dtype == RI_DTYPE_BF16)
+            ri_launch_pdl(moe_route_wide_kernel<bf16>, dim3(tokens), dim3(MOE_ROUTE_WIDE_THREADS), sm, stream, (const bf16*)x,
+                          router, correction, idx, weight, D, N, top);
+        else RI_FAIL(-1, "moe_route: unknown dtype %d", dtype);
+        RI_CHECK_LAUNCH("moe_route");
+        return 0;
+    }
     if (dtype == RI_DTYPE_F32) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RI_FAIL((int)e, "moe_route: %s", cudaGetErrorString(e));
         ri_launch_pdl(moe_route_kernel<float>, grid, dim3(32 * MOE_ROUTE_WARPS), smem, stream, (const float*)x, router,
-                      correction, idx, weight, tokens, D, N, top);
+                      correction, idx, weight, tokens, D, N, top, vec);
     } else if (dtype == RI_DTYPE_BF16) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RI_FAIL((int)e, "moe_route: %s", cudaGetErrorString(e));
         ri_launch_pdl(moe_route_kernel<bf16>, grid, dim3(32 * MOE_ROUTE_WARPS), smem, stream, (const bf16*)x, router,
-                      correction, idx, weight, tokens, D, N, top);
+                      correction, idx, weight, tokens, D, N, top, vec);
     } else RI_FAIL(-1, "moe_route: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("moe_route");
     return 0;
