@@ -6,7 +6,9 @@ head, of a whole head, of nothing; convolutions of 4, 2 and 3 taps; fewer query/
 right; a routed feed-forward with an identity expert and a shared one, a dense one, a layer without feed-forward.
 B: a width that is no multiple of 8; heads of 64 on the left (the decode kernel for that size); a delta rule with 136
 key channels and a convolution of one tap; one expert per token, no identity expert, no shared one; a layer whose
-attention has no mask at all; low-rank projections of 5 and 3.  C: wider, for bfloat16.
+attention has no mask at all; low-rank projections of 5 and 3.  C: wider, for bfloat16.  D: a width that is no multiple
+of 4; head sizes that the kernels pad to 112 and 48; chunks of one position (a query sees itself and the sink); five taps;
+forty experts without a shared one; 130 value columns on 72 key channels.
 
 Weights are made here, with activations of order one (so that attention is far from uniform and a chunk's edge, a
 sink or a lost state shows), rounded to bfloat16 and stored as bfloat16.
@@ -72,7 +74,15 @@ CFG_C = {
                _moe(6, 2, 3, 64, 1.0, shared=(96, 1.5))),
     ],
 }
-ALL = {"A": (CFG_A, (6, 10)), "B": (CFG_B, (5, 3)), "C": (CFG_C, (16, 8))}
+CFG_D = {
+    "architecture": "Pitenex", "vocab": 61, "width": 50, "embedding": {"bigram": {"buckets": 7, "mul_prev": 1, "mul_cur": 1}},
+    "norm": {"eps": 1e-4}, "residual_mult": 0.9, "logit_scale": 1.0,
+    "layers": [
+        _layer(_left(2, 1, 96, 112, size=20, rot=10, base=7.0), _right(3, 3, 20, 12, 5), 1.0, 0.8, _moe(40, 0, 3, 8, 1.1)),
+        _layer(_left(6, 2, 40, 24, size=1), _right(2, 1, 72, 130, 2), 0.5, 1.5, {"kind": "dense", "ff": 30}),
+    ],
+}
+ALL = {"A": (CFG_A, (6, 10)), "B": (CFG_B, (5, 3)), "C": (CFG_C, (16, 8)), "D": (CFG_D, (2, 4))}
 
 
 def make_weights(config, seed, ranks=(6, 10)):

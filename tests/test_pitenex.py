@@ -84,7 +84,7 @@ def test_chunked_groups_give_pages_back():
     assert pt.release_behind_window(0) == 3                                   # next query at 23: chunk starts at 20
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_replay_three_ways_matches_plain(tmp_path, emulated_ops, name):
     d, config, weights = R.make_model_dir(tmp_path, name, seed=3)
     rng = np.random.default_rng(4)

@@ -297,6 +297,13 @@ def test_router_choice_weights_and_ties():
     chosen, weight = P.route(_np(x), _np(router), _np(corr), top)
     assert np.array_equal(idx.cpu().numpy(), chosen)
     _close(w, weight, torch.float32, "weights", tol32=1e-5)
+    # a router too large for the kernel that takes a block per token, and rows that are no whole 16-byte pieces
+    for T2, D2, N2 in ((5, 4096, 300), (9, 50, 13)):
+        x2, r2, c2 = _t(rng.standard_normal((T2, D2))), _t(rng.standard_normal((N2, D2)) * 0.1), _t(rng.uniform(-0.05, 0.05, N2))
+        idx, w = ops.moe_route(x2, r2, c2, 5)
+        chosen, weight = P.route(_np(x2), _np(r2), _np(c2), 5)
+        assert np.array_equal(idx.cpu().numpy(), chosen)
+        _close(w, weight, torch.float32, "weights", tol32=1e-4)
     # equal choice scores: the lower index first; the correction changes the choice but not the weights
     router0 = torch.zeros((6, D), device=DEV)
     idx, w = ops.moe_route(x[:3].contiguous(), router0, torch.zeros(6, device=DEV), 3)
@@ -349,7 +356,7 @@ def _portions(reqs, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_in_five_cuttings_matches_plain(tmp_path, name, dtype):
     d, config, weights = R.make_model_dir(tmp_path, name, seed=3)
     rng = np.random.default_rng(4)
