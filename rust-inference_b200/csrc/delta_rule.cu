@@ -52,6 +52,63 @@ short_conv_kernel(const T* __restrict__ x, long long ld, int col0, const float* 
     }
 }
 
+// bfloat16 inputs, eight neighbouring channels per thread (16-byte loads of the inputs, of the weights in their
+// transposed copy wt [taps, C], of the state; two 16-byte stores): an element's arithmetic and its order are the scalar
+// kernel's.  For C, ld and col0 multiples of 8 and 16-byte aligned bases.
+__global__ void __launch_bounds__(128)
+short_conv_x8_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int col0, const float* __restrict__ wt,
+                     float* __restrict__ y, float* __restrict__ state, const int* __restrict__ tok_seq,
+                     const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int C, int taps, int update) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    const int t = blockIdx.x;
+    if (c >= C) return;
+    const int b = tok_seq[t];
+    const int t0 = seq_start[b];
+    float* st = state + (size_t)seq_slot[b] * (taps - 1) * C + c;
+    float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    float cur[8];
+    for (int j = 0; j < taps; j++) {
+        const int r = (t - t0) - (taps - 1 - j);
+        float v[8];
+        if (r >= 0) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * ld + col0 + c);
+            const unsigned u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                v[2 * e] = __uint_as_float(u[e] << 16);
+                v[2 * e + 1] = __uint_as_float(u[e] & 0xffff0000u);
+            }
+        } else {
+            const float4 a = *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 + r) * C);
+            const float4 bq = *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 + r) * C + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = bq.x; v[5] = bq.y; v[6] = bq.z; v[7] = bq.w;
+        }
+        const float4 w0 = *reinterpret_cast<const float4*>(wt + (size_t)j * C + c);
+        const float4 w1 = *reinterpret_cast<const float4*>(wt + (size_t)j * C + c + 4);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            acc[e] = fmaf(wv[e], v[e], acc[e]);
+            cur[e] = v[e];                                        // after the last tap: the current token's inputs
+        }
+    }
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) o[e] = dr_silu(acc[e]);
+    *reinterpret_cast<float4*>(y + (size_t)t * C + c) = make_float4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<float4*>(y + (size_t)t * C + c + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    if (update && taps > 1) {
+        for (int j = 0; j + 1 < taps - 1; j++) {
+            *reinterpret_cast<float4*>(st + (size_t)j * C) = *reinterpret_cast<const float4*>(st + (size_t)(j + 1) * C);
+            *reinterpret_cast<float4*>(st + (size_t)j * C + 4) = *reinterpret_cast<const float4*>(st + (size_t)(j + 1) * C + 4);
+        }
+        *reinterpret_cast<float4*>(st + (size_t)(taps - 2) * C) = make_float4(cur[0], cur[1], cur[2], cur[3]);
+        *reinterpret_cast<float4*>(st + (size_t)(taps - 2) * C + 4) = make_float4(cur[4], cur[5], cur[6], cur[7]);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 short_conv_state_kernel(const T* __restrict__ x, long long ld, int col0, float* __restrict__ state,
@@ -69,7 +126,8 @@ short_conv_state_kernel(const T* __restrict__ x, long long ld, int col0, float* 
     }
 }
 
-extern "C" int ri_short_conv(const void* x, long long ld, int col0, const float* w, float* y, float* state,
+// wt: the weights once more as [taps, C] (may be null: then the scalar kernel runs)
+extern "C" int ri_short_conv(const void* x, long long ld, int col0, const float* w, const float* wt, float* y, float* state,
                              const int* tok_seq, const int* seq_slot, const int* seq_start, int tokens, int seqs, int C,
                              int taps, int single, int dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
@@ -78,7 +136,12 @@ extern "C" int ri_short_conv(const void* x, long long ld, int col0, const float*
     RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "short_conv: unknown dtype %d", dtype);
     const int upd = single && tokens == seqs ? 1 : 0;
     const dim3 grid(tokens, (C + 255) / 256);
-    if (dtype == RI_DTYPE_F32)
+    const bool x8 = dtype == RI_DTYPE_BF16 && wt && C % 8 == 0 && ld % 8 == 0 && col0 % 8 == 0 &&
+                    (((uintptr_t)x | (uintptr_t)wt | (uintptr_t)y | (uintptr_t)state) & 15) == 0;
+    if (x8)
+        ri_launch_pdl(short_conv_x8_kernel, dim3(tokens, (C / 8 + 127) / 128), dim3(128), 0, stream, (const __nv_bfloat16*)x, ld,
+                      col0, wt, y, state, tok_seq, seq_slot, seq_start, C, taps, upd);
+    else if (dtype == RI_DTYPE_F32)
         ri_launch_pdl(short_conv_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, ld, col0, w, y, state, tok_seq,
                       seq_slot, seq_start, tokens, C, taps, upd);
     else

@@ -29,7 +29,7 @@ _SIGNATURES = {
     ("streams", "ri_stream_norm"): [_P] * 8 + [_I, _I, _I, _F, _I, _I, _P],
     ("streams", "ri_stream_norm2"): [_P] * 13 + [_I, _I, _I, _F, _I, _I, _P],
     ("pair_embedding", "ri_embed_pair_hash"): [_P] * 9 + [_I, _I, _I, _I, _I, _L, _L, _I, _I, _P, _P],
-    ("delta_rule", "ri_short_conv"): [_P, _L, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    ("delta_rule", "ri_short_conv"): [_P, _L, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     ("delta_rule", "ri_delta_rule_recurrent"): [_P, _I, _I, _I, _I, _P, _L, _I, _P, _P, _P, _F] + [_P] * 6 + [_I] * 8 + [_P],
     ("elementwise", "ri_gated_act"): [_P, _P, _I, _I, _I, _I, _F, _F, _I, _P],
     ("elementwise", "ri_scale_f32"): [_P, _L, _F, _P],
@@ -875,10 +875,13 @@ def embed_pair_hash(ids: torch.Tensor, table: torch.Tensor, pairs: torch.Tensor,
 
 
 def short_conv(x: torch.Tensor, col0: int, weight: torch.Tensor, state: torch.Tensor, tok_seq: torch.Tensor,
-               seq_slot: torch.Tensor, seq_start: torch.Tensor, single: bool = False) -> torch.Tensor:
+               seq_slot: torch.Tensor, seq_start: torch.Tensor, single: bool = False,
+               weight_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal convolution over time per channel, then silu: channels are columns ``col0 .. col0 + C`` of ``x``
     [tokens, N]; ``weight`` [C, taps] float32 (the last column is the current token's); ``state`` [slots, taps-1, C]
-    float32 holds every sequence's last inputs (zeros at its start) and is brought up to date.  float32 [tokens, C]."""
+    float32 holds every sequence's last inputs (zeros at its start) and is brought up to date.  ``weight_t``: the
+    weights once more as [taps, C]; with it bfloat16 inputs take a kernel of eight channels per thread (the same
+    results).  float32 [tokens, C]."""
     _need(x, "x")
     _need(weight, "weight", torch.float32)
     C, taps = weight.shape
@@ -892,7 +895,9 @@ def short_conv(x: torch.Tensor, col0: int, weight: torch.Tensor, state: torch.Te
     for t, n in ((tok_seq, "tok_seq"), (seq_slot, "seq_slot"), (seq_start, "seq_start")):
         _need(t, n, torch.int32)
     y = torch.empty((tokens, C), dtype=torch.float32, device=x.device)
-    _call("delta_rule", "ri_short_conv", x.data_ptr(), ld, int(col0), weight.data_ptr(), y.data_ptr(), state.data_ptr(),
+    if weight_t is not None:
+        _need(weight_t, "weight_t", torch.float32, (taps, C))
+    _call("delta_rule", "ri_short_conv", x.data_ptr(), ld, int(col0), weight.data_ptr(), _ptr(weight_t), y.data_ptr(), state.data_ptr(),
           tok_seq.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), tokens, seqs, C, taps, 1 if single else 0,
           _code(x.dtype), _stream())
     if not (single and tokens == seqs) and taps > 1:

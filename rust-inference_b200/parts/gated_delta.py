@@ -70,6 +70,7 @@ class GatedDeltaRule(Mixer):
         self.g_col = self.a_col + blocks[2].shape[0]
         self.a_rank, self.g_rank = blocks[2].shape[0], blocks[3].shape[0]
         self.conv = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).contiguous()
+        self.conv_t = self.conv.t().contiguous()            # [taps, channels]: what the kernel of eight channels per thread reads
         self.a2, self.g2 = cols8(tensors["a2"]).contiguous(), cols8(tensors["g2"]).contiguous()
         self.dt_bias, self.a_log, self.gain = tensors["dt_bias"], tensors["A_log"], tensors["norm"]
         self.o = tensors["o"].contiguous()
@@ -96,7 +97,8 @@ class GatedDeltaRule(Mixer):
             za = ops.linear(proj[:, self.a_col:self.a_col + self.a_rank].contiguous(), self.a2)
             zg = ops.linear(proj[:, self.g_col:self.g_col + self.g_rank].contiguous(), self.g2)
         with section("delta conv"):
-            qkv = ops.short_conv(proj, 0, self.conv, cache.more_state[0], ctx.tok_seq, ctx.seq_slot, ctx.seq_start, single=single)
+            qkv = ops.short_conv(proj, 0, self.conv, cache.more_state[0], ctx.tok_seq, ctx.seq_slot, ctx.seq_start, single=single,
+                                 weight_t=self.conv_t)
         with section("delta recurrence"):
             o = ops.delta_rule_recurrent(qkv, self.q_col, self.k_col, self.v_col, proj, self.b_col, za, self.dt_bias, self.a_log,
                                          s.dim ** -0.5, cache.state, ctx.seq_slot, ctx.seq_start, H, s.num_qk_heads, s.dim,

@@ -277,7 +277,7 @@ def embed_pair_hash(ids, table, pairs, last_token, tok_seq, tok_pos, seq_slot, s
     return out
 
 
-def short_conv(x, col0, weight, state, tok_seq, seq_slot, seq_start, single=False):
+def short_conv(x, col0, weight, state, tok_seq, seq_slot, seq_start, single=False, weight_t=None):
     C, taps = weight.shape
     xin = x[:, col0:col0 + C].float()
     y = torch.zeros(x.shape[0], C)

@@ -100,9 +100,10 @@ def test_layer_norm_with_bias_and_three_pending_outputs(dim, n, dtype):
 def test_short_conv_whole_in_portions_and_token_by_token(taps, dtype):
     from rust_inference_b200 import ops
     rng = np.random.default_rng(taps)
-    C, n, col0 = 70, 23, 8
-    x = _t(rng.standard_normal((n, col0 + C + 5)), dtype)
+    C, n, col0 = (72, 23, 8) if taps == 4 else (70, 23, 8)         # 72 channels in a matrix of 88 columns: eight per thread
+    x = _t(rng.standard_normal((n, col0 + C + (8 if taps == 4 else 5))), dtype)
     w = _t(rng.uniform(-0.8, 0.8, (C, taps)))
+    wt = w.t().contiguous()
     want = P.short_conv(_np(x)[:, col0:col0 + C], _np(w))
     results = {}
     for label, cuts in (("whole", [n]), ("portions", [2, 1, 7, 2, 11]), ("single", [1] * n)):
@@ -111,7 +112,8 @@ def test_short_conv_whole_in_portions_and_token_by_token(taps, dtype):
         outs, at = [], 0
         for c in cuts:
             tok_seq, seq_start = _tables([c])
-            outs.append(ops.short_conv(x[at:at + c].contiguous(), col0, w, state, tok_seq, _i([1]), seq_start, single=(c == 1)))
+            outs.append(ops.short_conv(x[at:at + c].contiguous(), col0, w, state, tok_seq, _i([1]), seq_start, single=(c == 1),
+                                       weight_t=wt if label != "portions" else None))
             at += c
         results[label] = torch.cat(outs)
         _close(results[label], want, torch.float32, f"{label}, {taps} taps", tol32=1e-5)
