@@ -289,15 +289,15 @@ def pitenex_config(z) -> dict:
             "rot": {"base": 500000.0, "dims": 64}, "mask": {"size": 2048}}
     right = {"heads": max(1, H // 2), "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64,
              "gate_rank": 64}
-    mixer = {"left": left, "right": right, "left_scale": 0.8, "right_scale": 1.1}
+    mixer = {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}
     inter = -(-(2 * z["ff"] // 3) // 256) * 256          # three matrices of a gated feed-forward against two
     dense = {"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": inter}}
     moe = {"type": "parallel", "mixer": mixer,
            "mlp": {"kind": "moe", "router": {"experts": 16, "identity": 2, "top": 4},
                    "expert": {"ff": inter // 8, "limit": 7.0}, "shared": {"ff": inter // 4, "limit": 7.0}}}
     return {"architecture": "Pitenex", "vocab": z["vocab"], "width": D,
-            "embedding": {"bigram": {"buckets": 8191, "mul_prev": 127, "mul_cur": 7}}, "norm": {"eps": 1e-6},
-            "residual_mult": 0.7, "logit_scale": 1.0, "layers": [dense, moe] * (z["layers"] // 2)}
+            "embedding": {"bigram": {"buckets": 8191, "mul_prev": 131, "mul_cur": 11}}, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "logit_scale": 1.0, "layers": [dense, moe] * (z["layers"] // 2)}
 
 
 DESIGNS = {"ranudra": ranudra_config, "pitenex": pitenex_config}

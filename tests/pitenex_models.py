@@ -23,7 +23,7 @@ import plain_pitenex
 from ranudra_models import _bf16, row_error, write_model
 
 
-def _left(heads, kv, dim, vdim, size=None, rot=None, base=10000.0, scale=None):
+def _left(heads, kv, dim, vdim, size=None, rot=None, base=1000.0, scale=None):
     m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale if scale is not None else dim ** -0.5}
     if rot:
         m["rot"] = {"base": base, "dims": rot}
@@ -69,7 +69,7 @@ CFG_C = {
     "architecture": "Pitenex", "vocab": 300, "width": 128, "embedding": {"bigram": {"buckets": 211, "mul_prev": 13, "mul_cur": 1}},
     "norm": {"eps": 1e-6}, "residual_mult": 0.5, "logit_scale": 3.0,
     "layers": [
-        _layer(_left(4, 2, 32, 48, size=48, rot=16, base=10000.0), _right(4, 2, 64, 32, 3), 0.8, 1.1, {"kind": "dense", "ff": 160}),
+        _layer(_left(4, 2, 32, 48, size=48, rot=16, base=20000.0), _right(4, 2, 64, 32, 3), 0.75, 1.25, {"kind": "dense", "ff": 160}),
         _layer(_left(8, 1, 128, 128, size=100, rot=128, base=500.0), _right(2, 2, 24, 96, 4), 1.0, 0.6,
                _moe(6, 2, 3, 64, 1.0, shared=(96, 1.5))),
     ],

@@ -200,7 +200,7 @@ def _plain_chunked(q, k, v, sink, scale, size, positions):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("D, size", [(32, 7), (80, 33), (64, 96), (128, 40)])
+@pytest.mark.parametrize("D, size", [(32, 7), (80, 33), (64, 90), (128, 40)])
 def test_chunked_attention_with_a_loud_key_at_the_edges(D, size, dtype):
     """One key is made loud (its score stands out among hundreds).  Queries just inside its chunk must follow its value,
     queries just outside must not see it; in a prompt, in a portion of a prompt, and token by token."""
