@@ -113,7 +113,9 @@ class PageTable:
     stored per slot.
 
     ``window`` > 0: only the last ``window`` keys are ever read again, so pages
-    that lie wholly before them are released after every step.  ``handle``: a
+    that lie wholly before them are released after every step.  ``window`` < 0: a
+    mask of chunks of ``-window`` positions counted from the sequence's start; the
+    pages before the chunk of the next query are released.  ``handle``: a
     group of a whole cache, which that cache owns.
     """
 
