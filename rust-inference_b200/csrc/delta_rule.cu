@@ -351,7 +351,7 @@ extern "C" int ri_delta_rule_recurrent(float* qkv, int C, int q_col, int k_col, 
     if (seqs == 0 || tokens == 0) return 0;
     RI_REQUIRE(seqs > 0 && tokens > 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0, "delta_rule_recurrent: bad sizes");
     RI_REQUIRE(seqs <= 65535 && H <= 65535, "delta_rule_recurrent: %d sequences, %d heads: too many for one launch", seqs, H);
-    RI_REQUIRE(dim <= 256, "delta_rule_recurrent: %d key channels per head (up to 256 are built)", dim);
+    RI_REQUIRE(dim <= 512, "delta_rule_recurrent: %d key channels per head (up to 512 are built)", dim);
     const int spread = tokens >= 256 ? 1 : (H * dim + 127) / 128 > 16 ? 16 : (H * dim + 127) / 128;
     const dim3 pgrid(tokens, spread);
     if (dtype == RI_DTYPE_F32)
@@ -383,7 +383,8 @@ extern "C" int ri_delta_rule_recurrent(float* qkv, int C, int q_col, int k_col, 
     else if (dim <= 32) DR_BY_GROUP(4, 8, 16);
     else if (dim <= 64) DR_BY_GROUP(4, 16, 16);
     else if (dim <= 128) DR_BY_GROUP(8, 16, 8);
-    else DR_BY_GROUP(16, 16, 4);
+    else if (dim <= 256) DR_BY_GROUP(16, 16, 4);
+    else DR_BY_GROUP(32, 16, 2);
 #undef DR_BY_GROUP
 #undef DR_GO
     RI_CHECK_LAUNCH("delta_rule_recurrent");

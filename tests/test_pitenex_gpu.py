@@ -125,7 +125,7 @@ def test_short_conv_whole_in_portions_and_token_by_token(taps, dtype):
 
 # ---- the recurrence ------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H, G, dim, vdim", [(4, 2, 12, 20), (2, 2, 136, 16), (1, 1, 64, 70), (3, 1, 200, 8)])
+@pytest.mark.parametrize("H, G, dim, vdim", [(4, 2, 12, 20), (2, 2, 136, 16), (1, 1, 64, 70), (3, 1, 200, 8), (1, 1, 300, 9)])
 def test_delta_rule_against_the_plain_recurrence(H, G, dim, vdim, dtype):
     from rust_inference_b200 import ops
     rng = np.random.default_rng(H * dim)
