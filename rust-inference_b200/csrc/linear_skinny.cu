@@ -197,7 +197,10 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
                 g += sm.part[wi][r][tok];
                 u += sm.part[wi][r + 8][tok];
             }
-            st_f(y + (size_t)tok * (N / 2) + n0 / 2 + r, (g / (1.0f + expf(-g))) * u);
+            // the gate's function: silu, or (act 2) gelu in its tanh form
+            const float fg = act == 2 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                                      : g / (1.0f + expf(-g));
+            st_f(y + (size_t)tok * (N / 2) + n0 / 2 + r, fg * u);
         }
     } else {
         for (int i = threadIdx.x; i < SK_ROWS * NT * 8; i += blockDim.x) {
@@ -320,6 +323,20 @@ extern "C" int ri_linear_skinny_act(const void* x, const void* w, void* y, int M
     } else {
         rc = out_f32 ? launch_skinny<2, float, false>(x, w, y, M, N, K, act, err_flag, stream) : launch_skinny<2, bf16, false>(x, w, y, M, N, K, act, err_flag, stream);
     }
+    if (rc) return rc;
+    RI_CHECK_LAUNCH("linear_skinny");
+    return 0;
+}
+
+// The gated epilogue with another function of the gate: y [M, N/2] = f(gate) * up, gate 0 = silu, 2 = gelu in its tanh form.
+extern "C" int ri_linear_skinny_gated(const void* x, const void* w, void* y, int M, int N, int K, int gate, int* err_flag,
+                                      cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    RI_REQUIRE(gate == 0 || gate == 2, "linear_skinny: gate function %d (0 silu, 2 gelu_tanh)", gate);
+    RI_REQUIRE(M > 0 && M <= 16 && N > 0 && K > 0 && K % 8 == 0 && N % 16 == 0, "linear_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
+    RI_REQUIRE((((uintptr_t)x | (uintptr_t)w) & 15) == 0, "linear_skinny: x and w must be 16-byte aligned");
+    const int rc = M <= 8 ? launch_skinny<1, bf16, true>(x, w, y, M, N, K, gate, err_flag, stream)
+                          : launch_skinny<2, bf16, true>(x, w, y, M, N, K, gate, err_flag, stream);
     if (rc) return rc;
     RI_CHECK_LAUNCH("linear_skinny");
     return 0;

@@ -287,6 +287,14 @@ def test_gates(dtype):
         _close(ops.gated_act(gu, "gelu_tanh", block), P.gelu_tanh(g) * u, dtype, "gelu")
         gc, uc = np.minimum(g, 0.9), np.clip(u, -0.9, 0.9)
         _close(ops.gated_act(gu, "clamped_swish", block, 0.9, 1.702), gc * P.sigmoid(1.702 * gc) * (uc + 1), dtype, "clamped swish")
+    # the gelu gate behind a product: in the weight-streaming product's epilogue for a handful of bfloat16 tokens, else after it
+    inter, K = 40, 64
+    wg, wu = _t(rng.standard_normal((inter, K)) * 0.3, dtype), _t(rng.standard_normal((inter, K)) * 0.3, dtype)
+    stacked = torch.stack([wg.view(inter // 8, 8, K), wu.view(inter // 8, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
+    for m in (3, 12, 70):
+        xin = _t(rng.standard_normal((m, K)), dtype)
+        want = P.gelu_tanh(_np(xin) @ _np(wg).T) * (_np(xin) @ _np(wu).T)
+        _close(ops.linear_gated(xin, stacked, 8, "gelu_tanh"), want, dtype, f"gelu-gated product of {m} tokens")
 
 
 def test_router_choice_weights_and_ties():
